@@ -19,7 +19,9 @@ from typing import Dict, List, Optional
 
 import torch
 
-from yalis_b200.parts.base import PagedKV, PagedKVCache, SlotState, SlotStateCache
+from collections.abc import Mapping
+
+from yalis_b200.parts.base import PagedKV, PagedKVCache, SlotState, SlotStateCache, cache_leaves
 from .manager import PageGroup
 
 
@@ -34,10 +36,11 @@ def group_page_bytes(requests: List[Optional[object]], cache_of: List[Optional[i
     """Bytes that one page id of each group stands for: the K and V pages of every schedule entry of the group
     that keeps a cache of its own."""
     out: Dict[str, int] = {}
-    for req, src in zip(requests, cache_of):
-        if isinstance(req, PagedKV) and src is None:
-            name = group_name(req)
-            out[name] = out.get(name, 0) + 2 * req.num_kv_heads * page_size * req.head_dim * element_size
+    for top, src in zip(requests, cache_of):
+        for req in cache_leaves(top):
+            if isinstance(req, PagedKV) and src is None:
+                name = group_name(req)
+                out[name] = out.get(name, 0) + req.num_kv_heads * page_size * (req.head_dim + req.value_dim) * element_size
     return out
 
 
@@ -55,7 +58,7 @@ def plan_groups(requests: List[Optional[object]], page_size: int, num_pages: int
     (``window_group_pages``) when ``max_slots`` and ``step_tokens`` are known."""
     groups: Dict[str, PageGroup] = {}
     width = -(-max_context // page_size)
-    for r in requests:
+    for r in (leaf for top in requests for leaf in cache_leaves(top)):
         if isinstance(r, PagedKV):
             name = group_name(r)
             if name not in groups:
@@ -71,39 +74,49 @@ class CacheStorage:
 
     def __init__(self, requests: List[Optional[object]], cache_of: List[Optional[int]], groups: List[PageGroup],
                  max_slots: int, device, dtype: torch.dtype):
-        by_name = {g.name: g for g in groups}
+        self._by_name = {g.name: g for g in groups}
+        self._max_slots, self._device, self._dtype = max_slots, device, dtype
         self.entries: List[Optional[object]] = []
         self.state_tensors: List[torch.Tensor] = []
         self.bytes = 0
         for i, (req, src) in enumerate(zip(requests, cache_of)):
             if src is not None:
-                own = self.entries[src]
-                if isinstance(own, PagedKVCache):
-                    if not isinstance(req, PagedKV) or (req.num_kv_heads, req.head_dim) != (own.k.shape[1], own.k.shape[3]):
-                        raise ValueError(f"schedule entry {i} cannot read the cache of entry {src}: shapes differ")
-                    self.entries.append(PagedKVCache(own.k, own.v, own.group, writable=False))
-                elif isinstance(own, SlotStateCache):
-                    self.entries.append(SlotStateCache(own.state, writable=False))
-                else:
-                    raise ValueError(f"schedule entry {i} reads the cache of entry {src}, which keeps none")
-                continue
-            if req is None:
-                self.entries.append(None)
-            elif isinstance(req, PagedKV):
-                g = by_name[group_name(req)]
-                shape = (g.num_pages, req.num_kv_heads, g.page_size, req.head_dim)
-                k = torch.empty(shape, dtype=dtype, device=device)
-                v = torch.empty(shape, dtype=dtype, device=device)
-                self.bytes += 2 * k.numel() * k.element_size()
-                self.entries.append(PagedKVCache(k, v, g.name))
-            elif isinstance(req, SlotState):
-                # one row more than there are slots: the row that padding rows of a recorded step point to
-                st = torch.zeros((max_slots + 1,) + tuple(req.shape), dtype=req.dtype, device=device)
-                self.bytes += st.numel() * st.element_size()
-                self.state_tensors.append(st)
-                self.entries.append(SlotStateCache(st))
+                self.entries.append(self._reader(i, src, req, self.entries[src]))
             else:
-                raise TypeError(f"schedule entry {i}: unknown cache request {req!r}")
+                self.entries.append(self._allocate(i, req))
+
+    def _reader(self, i: int, src: int, req, own):
+        """The cache of entry ``src`` as entry ``i`` may use it: read, never written."""
+        if isinstance(own, dict):
+            if not isinstance(req, Mapping) or set(req) != set(own):
+                raise ValueError(f"schedule entry {i} cannot read the cache of entry {src}: they keep different things")
+            return {name: self._reader(i, src, req[name], own[name]) for name in own}
+        if isinstance(own, PagedKVCache):
+            if not isinstance(req, PagedKV) or (req.num_kv_heads, req.head_dim, req.value_dim) != (own.k.shape[1], own.k.shape[3], own.v.shape[3]):
+                raise ValueError(f"schedule entry {i} cannot read the cache of entry {src}: shapes differ")
+            return PagedKVCache(own.k, own.v, own.group, writable=False)
+        if isinstance(own, SlotStateCache):
+            return SlotStateCache(own.state, writable=False)
+        raise ValueError(f"schedule entry {i} reads the cache of entry {src}, which keeps none")
+
+    def _allocate(self, i: int, req):
+        if req is None:
+            return None
+        if isinstance(req, Mapping):
+            return {name: self._allocate(i, sub) for name, sub in req.items()}
+        if isinstance(req, PagedKV):
+            g = self._by_name[group_name(req)]
+            k = torch.empty((g.num_pages, req.num_kv_heads, g.page_size, req.head_dim), dtype=self._dtype, device=self._device)
+            v = torch.empty((g.num_pages, req.num_kv_heads, g.page_size, req.value_dim), dtype=self._dtype, device=self._device)
+            self.bytes += k.numel() * k.element_size() + v.numel() * v.element_size()
+            return PagedKVCache(k, v, g.name)
+        if isinstance(req, SlotState):
+            # one row more than there are slots: the row that padding rows of a recorded step point to
+            st = torch.zeros((self._max_slots + 1,) + tuple(req.shape), dtype=req.dtype, device=self._device)
+            self.bytes += st.numel() * st.element_size()
+            self.state_tensors.append(st)
+            return SlotStateCache(st)
+        raise TypeError(f"schedule entry {i}: unknown cache request {req!r}")
 
     def reset_slot(self, slot: int) -> None:
         """Zero the per-request state of a newly admitted request."""

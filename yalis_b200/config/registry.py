@@ -9,7 +9,7 @@ An architecture is an object with
     (used by the random-weights mode to write a model folder).
 
 ``config.json`` names its architecture in ``architectures[0]`` (the Hugging Face
-convention); everything in the package that needs a model goes through
+convention) or in a string ``architecture``; everything in the package that needs a model goes through
 ``load_config`` / ``get_architecture``.  The reference looks models up by a
 name registry of dictionaries instead (yalis/external/config.py:183-205, 3249);
 its preset names are kept as aliases in ``yalis_b200.config.presets``.
@@ -54,14 +54,20 @@ def architecture_names() -> Tuple[str, ...]:
 
 def architecture_of(raw: Dict[str, Any]) -> str:
     archs = raw.get("architectures")
+    if archs is None and isinstance(raw.get("architecture"), str):
+        return raw["architecture"]           # the form of configurations that name one design
     if not archs or not isinstance(archs, (list, tuple)) or not isinstance(archs[0], str):
         raise ConfigError("config.json has no `architectures` entry naming the model class")
     return archs[0]
 
 
-def parse_config(raw: Dict[str, Any]):
-    """(architecture object, typed config) for the dictionary of a config.json."""
+def parse_config(raw: Dict[str, Any], tensor_shapes=None):
+    """(architecture object, typed config) for the dictionary of a config.json.  ``tensor_shapes`` (name -> shape,
+    from a checkpoint's header) goes to architectures whose configuration leaves sizes to the tensors
+    (``sizes_from_tensors(raw, shapes) -> raw``)."""
     arch = get_architecture(architecture_of(raw))
+    if tensor_shapes is not None and hasattr(arch, "sizes_from_tensors"):
+        raw = arch.sizes_from_tensors(raw, tensor_shapes)
     return arch, arch.parse_config(raw)
 
 
@@ -71,9 +77,14 @@ def load_config(model_dir: str):
         raise FileNotFoundError(f"no config.json in {model_dir}")
     with open(path) as f:
         raw = json.load(f)
-    return parse_config(raw)
+    shapes = None
+    if hasattr(get_architecture(architecture_of(raw)), "sizes_from_tensors"):
+        from yalis_b200.weights.safetensors_io import Checkpoint
+        with Checkpoint(model_dir) as ckpt:
+            shapes = {name: tuple(ckpt.info(name)[1]) for name in ckpt.names()}
+    return parse_config(raw, shapes)
 
 
 def _ensure_builtin() -> None:
     # Importing the module registers the architecture it defines.
-    from yalis_b200.models import llama  # noqa: F401
+    from yalis_b200.models import llama, tirezen  # noqa: F401

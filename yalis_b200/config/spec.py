@@ -58,12 +58,25 @@ class LayerSpec:
 
 
 @dataclass(frozen=True)
+class StreamInjection:
+    """What is added to the residual stream before a schedule entry runs: the embedding rows of the step's
+    tokens as they entered the stream (``embedding``), and row ``row`` of the model-level tensor ``vector``
+    ([rows, hidden], named in ``ModelSpec.extra_tensors``), the same for every token."""
+
+    embedding: bool = False
+    vector: Optional[str] = None
+    row: int = 0
+
+
+@dataclass(frozen=True)
 class ScheduleEntry:
     """Run layer ``layer``.  ``cache_of`` = index of an earlier schedule entry
-    whose cache this entry reads instead of keeping its own (None: own cache)."""
+    whose cache this entry reads instead of keeping its own (None: own cache).
+    ``before``: an addition to the stream that precedes the layer."""
 
     layer: int
     cache_of: Optional[int] = None
+    before: Optional[StreamInjection] = None
 
 
 @dataclass(frozen=True)
@@ -82,6 +95,8 @@ class ModelSpec:
     bos_token_id: Optional[int] = None
     embedding_scale: Optional[float] = None   # token rows are multiplied by it as they enter the stream (None: not)
     logit_softcap: Optional[float] = None     # logits become cap * tanh(logits / cap) (None: not)
+    # tensors that belong to no layer: local name -> (tensor name in the checkpoint, shape); held in float32
+    extra_tensors: Mapping[str, Tuple[str, Tuple[int, ...]]] = field(default_factory=dict)
 
     def __post_init__(self):
         for i, e in enumerate(self.schedule):
@@ -89,6 +104,11 @@ class ModelSpec:
                 raise ValueError(f"schedule entry {i} names layer {e.layer}, but there are {len(self.layers)} layers")
             if e.cache_of is not None and not 0 <= e.cache_of < i:
                 raise ValueError(f"schedule entry {i} reads the cache of entry {e.cache_of}, which does not run before it")
+            if e.before is not None and e.before.vector is not None:
+                if e.before.vector not in self.extra_tensors:
+                    raise ValueError(f"schedule entry {i} adds the tensor {e.before.vector!r}, which the model does not name")
+                if not 0 <= e.before.row < self.extra_tensors[e.before.vector][1][0]:
+                    raise ValueError(f"schedule entry {i} adds row {e.before.row} of {e.before.vector!r}, which has no such row")
 
 
 def default_schedule(n_layers: int) -> Tuple[ScheduleEntry, ...]:

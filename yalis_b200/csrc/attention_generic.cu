@@ -7,8 +7,10 @@
 // however the request was cut into steps.  It is the kernel of the float32
 // path and the twin against which the faster bfloat16 kernels are tested.
 //
-//   S = (q . k_j) / sqrt(hs) for keys j with  pos - window < j <= pos   (window 0: all j <= pos)
-//   O = softmax(S) V
+//   S = (q . k_j) * scale for keys j with  pos - window < j <= pos   (window 0: all j <= pos)
+//   S <- cap * tanh(S / cap)                                            (cap > 0 only)
+//   O = softmax(S) V, or with a sink: exp(S_j) / (1 + sum_i exp(S_i)) V  (a key of score 0 and no value)
+// Values may have a head size of their own (hsv).
 // Mask by absolute position: yalis/attention/backend_impl/sdpa_and_flex.py:15-19, 301-307.
 // KV head of query head h: h / (nh / g)                                 (:59-67).
 #include "common.cuh"
@@ -24,9 +26,10 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, int q_st
                                                const T* __restrict__ v_pool, const int32_t* __restrict__ positions,
                                                const int32_t* __restrict__ req_of_token,
                                                const int32_t* __restrict__ block_table, int table_width,
-                                               int page_size, int num_pages, int nh, int g, int hs, float scale,
-                                               int window) {
-  extern __shared__ float smem[];  // [kWarps][hs] accumulators, then m[kWarps], l[kWarps]
+                                               int page_size, int num_pages, int nh, int g, int hs, int hsv,
+                                               float scale, int window, float softcap, int sink,
+                                               float out_scale) {
+  extern __shared__ float smem[];  // [kWarps][hsv] accumulators, then m[kWarps], l[kWarps]
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
@@ -35,7 +38,7 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, int q_st
   const int pos = positions[t];
   const int kvh = h / (nh / g);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int per_lane = (hs + 31) >> 5;
+  const int per_lane = (hs + 31) >> 5, per_lane_v = (hsv + 31) >> 5;
 
   float qr[kMaxPerLane], acc[kMaxPerLane];
   const T* qp = q + (size_t)t * q_stride + (size_t)h * hs;
@@ -52,16 +55,17 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, int q_st
     const int pi = j / page_size;
     const int page = pi < table_width ? bt[pi] : -1;
     if (page < 0 || page >= num_pages) continue;  // unmapped: treated as masked
-    const size_t base = (((size_t)page * g + kvh) * page_size + (j - pi * page_size)) * hs;
-    const T* kp = k_pool + base;
-    const T* vp = v_pool + base;
+    const size_t row = ((size_t)page * g + kvh) * page_size + (j - pi * page_size);
+    const T* kp = k_pool + row * hs;
+    const T* vp = v_pool + row * hsv;
     float dot = 0.f;
 #pragma unroll
     for (int i = 0; i < kMaxPerLane; ++i) {
       const int d = lane + 32 * i;
       if (i < per_lane && d < hs) dot += qr[i] * to_f32<T>(kp[d]);
     }
-    const float s = warp_sum(dot) * scale;
+    float s = warp_sum(dot) * scale;
+    if (softcap > 0.f) s = softcap * tanhf(s / softcap);
     const float m_new = fmaxf(m, s);
     const float corr = expf(m - m_new);
     const float p = expf(s - m_new);
@@ -69,17 +73,17 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, int q_st
 #pragma unroll
     for (int i = 0; i < kMaxPerLane; ++i) {
       const int d = lane + 32 * i;
-      if (i < per_lane && d < hs) acc[i] = acc[i] * corr + p * to_f32<T>(vp[d]);
+      if (i < per_lane_v && d < hsv) acc[i] = acc[i] * corr + p * to_f32<T>(vp[d]);
     }
     m = m_new;
   }
   float* acc_s = smem;
-  float* m_s = smem + kWarps * hs;
+  float* m_s = smem + kWarps * hsv;
   float* l_s = m_s + kWarps;
 #pragma unroll
   for (int i = 0; i < kMaxPerLane; ++i) {
     const int d = lane + 32 * i;
-    if (i < per_lane && d < hs) acc_s[warp * hs + d] = acc[i];
+    if (i < per_lane_v && d < hsv) acc_s[warp * hsv + d] = acc[i];
   }
   if (lane == 0) {
     m_s[warp] = m;
@@ -89,19 +93,20 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, int q_st
   float mm = -INFINITY;
 #pragma unroll
   for (int w = 0; w < kWarps; ++w) mm = fmaxf(mm, m_s[w]);
-  float ll = 0.f;
+  if (sink) mm = fmaxf(mm, 0.f);
+  float ll = sink ? expf(-mm) : 0.f;
   float wgt[kWarps];
 #pragma unroll
   for (int w = 0; w < kWarps; ++w) {
     wgt[w] = (m_s[w] == -INFINITY) ? 0.f : expf(m_s[w] - mm);
     ll += l_s[w] * wgt[w];
   }
-  T* op = out + (size_t)t * out_stride + (size_t)h * hs;
-  for (int d = threadIdx.x; d < hs; d += blockDim.x) {
+  T* op = out + (size_t)t * out_stride + (size_t)h * hsv;
+  for (int d = threadIdx.x; d < hsv; d += blockDim.x) {
     float o = 0.f;
 #pragma unroll
-    for (int w = 0; w < kWarps; ++w) o += acc_s[w * hs + d] * wgt[w];
-    op[d] = from_f32<T>(ll > 0.f ? o / ll : 0.f);
+    for (int w = 0; w < kWarps; ++w) o += acc_s[w * hsv + d] * wgt[w];
+    op[d] = from_f32<T>(ll > 0.f ? o / ll * out_scale : 0.f);
   }
 }
 
@@ -111,16 +116,18 @@ YALIS_API int yalis_paged_attention_generic(const void* q, int q_stride, void* o
                                             const void* k_pool, const void* v_pool, int dtype,
                                             const int32_t* positions, const int32_t* req_of_token,
                                             const int32_t* block_table, int table_width, int page_size,
-                                            int num_pages, int n_tokens, int nh, int g, int hs, float scale,
-                                            int window, cudaStream_t stream) {
+                                            int num_pages, int n_tokens, int nh, int g, int hs, int hsv,
+                                            float scale, int window, float softcap, int sink, float out_scale,
+                                            cudaStream_t stream) {
   if (n_tokens <= 0) return YALIS_OK;
-  if (hs <= 0 || hs > 32 * kMaxPerLane || (hs & 1) || g <= 0 || nh % g != 0 || nh > 65535) return YALIS_ERR_SHAPE;
-  const size_t smem = ((size_t)kWarps * hs + 2 * kWarps) * sizeof(float);
+  if (hs <= 0 || hs > 32 * kMaxPerLane || hsv <= 0 || hsv > 32 * kMaxPerLane || g <= 0 || nh % g != 0 || nh > 65535)
+    return YALIS_ERR_SHAPE;
+  const size_t smem = ((size_t)kWarps * hsv + 2 * kWarps) * sizeof(float);
   dim3 grid(n_tokens, nh);
   YALIS_DISPATCH_DTYPE(dtype, T,
                        return yalis_launch(paged_attention_generic_kernel<T>, grid, dim3(kWarps * 32), smem, stream,
                                            (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pool,
                                            (const T*)v_pool, positions, req_of_token, block_table, table_width,
-                                           page_size, num_pages, nh, g, hs, scale, window));
+                                           page_size, num_pages, nh, g, hs, hsv, scale, window, softcap, sink, out_scale));
   return YALIS_OK;
 }

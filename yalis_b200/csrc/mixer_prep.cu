@@ -1,0 +1,178 @@
+// What lies between a mixer's input projection and its core, for mixers whose heads are
+// prepared in more ways than a full rotation: an added bias, a norm over the head with a
+// learned scale, a rotation of only the first `rot_dims` sizes, a constant factor, value heads
+// of a size of their own.  Queries go to a plain matrix; keys and values go to the pages of a
+// cache or to plain matrices (for mixers that keep a state instead of keys).  Also the
+// element-wise activations of dense feed-forwards and the row-wise additions of looped layers.
+// All arithmetic is float32; sines and cosines come from sincosf of a float32 angle.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kMaxHeadDim = 1024;
+
+struct PrepParams {
+  const void* src; int src_stride;           // [N, ...]: q heads at q_off, k heads at k_off, v heads at v_off
+  int q_off, k_off, v_off;
+  const void* q_bias; const void* k_bias; const void* v_bias;     // model dtype, or null
+  const float* q_norm; const float* k_norm; float norm_eps;       // scale over dim, or null: no norm
+  const float* inv_freq; int rot_dims;                            // [rot_dims / 2], or null: no rotation
+  float q_scale, k_scale;
+  void* q_out; int q_out_stride;             // [N, nq * dim]
+  void* k_out; int k_out_stride;             // plain destinations (used when k_pool is null)
+  void* v_out; int v_out_stride;
+  void* k_pool; void* v_pool;                // [pages, nk, page_size, dim] and [pages, nk, page_size, vdim]
+  const int32_t* block_table; int table_width, page_size, num_pages;
+  const int32_t* positions; const int32_t* req_of_token;
+  int nq, nk, dim, vdim;
+  int32_t* bad_page;
+};
+
+// One warp per (token, head): heads [0, nq) are queries, [nq, nq + nk) keys, [nq + nk, nq + 2 nk) values.
+template <typename T, typename TO>
+__global__ void qkv_prepare_kernel(const PrepParams p) {
+  __shared__ float xs[kMaxHeadDim];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int n = blockIdx.x, head = blockIdx.y, lane = threadIdx.x;
+  const int req = p.req_of_token[n];
+  if (req < 0) return;
+  const int pos = p.positions[n];
+  const bool is_q = head < p.nq, is_v = head >= p.nq + p.nk;
+  const int hh = is_q ? head : (is_v ? head - p.nq - p.nk : head - p.nq);
+  const int width = is_v ? p.vdim : p.dim;
+  const T* src = reinterpret_cast<const T*>(p.src) + (size_t)n * p.src_stride + (is_q ? p.q_off : (is_v ? p.v_off : p.k_off)) +
+                 (size_t)hh * width;
+  const T* bias = reinterpret_cast<const T*>(is_q ? p.q_bias : (is_v ? p.v_bias : p.k_bias));
+  TO* dst;
+  if (is_q) {
+    dst = reinterpret_cast<TO*>(p.q_out) + (size_t)n * p.q_out_stride + (size_t)hh * width;
+  } else if (p.k_pool != nullptr) {
+    const int page_idx = pos / p.page_size;
+    const int page = page_idx < p.table_width ? p.block_table[(size_t)req * p.table_width + page_idx] : -1;
+    if (page < 0 || page >= p.num_pages) {
+      if (lane == 0 && p.bad_page) atomicOr(p.bad_page, YALIS_FLAG_BAD_PAGE);
+      return;
+    }
+    dst = reinterpret_cast<TO*>(is_v ? p.v_pool : p.k_pool) +
+          (((size_t)page * p.nk + hh) * p.page_size + (pos - page_idx * p.page_size)) * width;
+  } else {
+    if (p.k_out == nullptr) return;              // nothing keeps this layer's keys and values: queries only
+    dst = is_v ? reinterpret_cast<TO*>(p.v_out) + (size_t)n * p.v_out_stride + (size_t)hh * width
+               : reinterpret_cast<TO*>(p.k_out) + (size_t)n * p.k_out_stride + (size_t)hh * width;
+  }
+  float ss = 0.f;
+  for (int d = lane; d < width; d += 32) {
+    float x = to_f32<T>(src[d]);
+    if (bias) x += to_f32<T>(bias[(size_t)hh * width + d]);
+    xs[d] = x;
+    ss = __fmaf_rn(x, x, ss);
+  }
+  if (is_v) {
+    for (int d = lane; d < width; d += 32) dst[d] = from_f32<TO>(xs[d]);
+    return;
+  }
+  const float* nw = is_q ? p.q_norm : p.k_norm;
+  if (nw) {
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss / (float)width + p.norm_eps);
+    for (int d = lane; d < width; d += 32) xs[d] = xs[d] * r * nw[d];
+  }
+  __syncwarp();
+  const float factor = is_q ? p.q_scale : p.k_scale;
+  const int half = p.inv_freq ? p.rot_dims >> 1 : 0;
+  for (int i = lane; i < half; i += 32) {
+    float sn, cs, o1, o2;
+    sincosf((float)pos * p.inv_freq[i], &sn, &cs);
+    rotate_pair(xs[i], xs[i + half], cs, sn, o1, o2);
+    dst[i] = from_f32<TO>(o1 * factor);
+    dst[i + half] = from_f32<TO>(o2 * factor);
+  }
+  for (int d = 2 * half + lane; d < width; d += 32) dst[d] = from_f32<TO>(xs[d] * factor);
+}
+
+// ACT: 0 gelu with erf, 1 gelu with tanh, 2 silu.
+template <typename T>
+__global__ void activation_kernel(const T* __restrict__ x, int x_stride, T* __restrict__ y, int y_stride, int rows,
+                                  int cols, int act) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t total = (size_t)rows * cols;
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = e / cols, c = e - r * cols;
+    const float z = to_f32<T>(x[r * x_stride + c]);
+    float o;
+    if (act == 0) o = 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
+    else if (act == 1) o = 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+    else o = silu_exact(z);
+    y[r * y_stride + c] = from_f32<T>(o);
+  }
+}
+
+// x[n, :] += other[n, :] + vec[:]   (either may be absent)
+__global__ void add_rows_vector_kernel(float* __restrict__ x, const float* __restrict__ other,
+                                       const float* __restrict__ vec, int rows, int cols) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t total = (size_t)rows * cols;
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+    float v = x[e];
+    if (other) v += other[e];
+    if (vec) v += vec[e % cols];
+    x[e] = v;
+  }
+}
+
+}  // namespace
+
+// out_dtype: the dtype of q_out and of the plain k_out / v_out (pools always have the model dtype `dtype`).
+YALIS_API int yalis_qkv_prepare(const void* src, int dtype, int src_stride, int q_off, int k_off, int v_off,
+                                const void* q_bias, const void* k_bias, const void* v_bias, const float* q_norm,
+                                const float* k_norm, float norm_eps, const float* inv_freq, int rot_dims, float q_scale,
+                                float k_scale, void* q_out, int q_out_stride, void* k_out, int k_out_stride, void* v_out,
+                                int v_out_stride, int out_dtype, void* k_pool, void* v_pool,
+                                const int32_t* block_table, int table_width, int page_size, int num_pages,
+                                const int32_t* positions, const int32_t* req_of_token, int n_tokens, int nq, int nk,
+                                int dim, int vdim, int32_t* bad_page, cudaStream_t stream) {
+  if (n_tokens <= 0) return YALIS_OK;
+  if (dim <= 0 || dim > kMaxHeadDim || vdim <= 0 || vdim > kMaxHeadDim || nq <= 0 || nk <= 0 || nq + 2 * nk > 65535)
+    return YALIS_ERR_SHAPE;
+  if (inv_freq && (rot_dims <= 0 || (rot_dims & 1) || rot_dims > dim)) return YALIS_ERR_SHAPE;
+  if (k_pool && out_dtype != dtype) return YALIS_ERR_DTYPE;
+  PrepParams p;
+  p.src = src; p.src_stride = src_stride; p.q_off = q_off; p.k_off = k_off; p.v_off = v_off;
+  p.q_bias = q_bias; p.k_bias = k_bias; p.v_bias = v_bias; p.q_norm = q_norm; p.k_norm = k_norm; p.norm_eps = norm_eps;
+  p.inv_freq = inv_freq; p.rot_dims = rot_dims; p.q_scale = q_scale; p.k_scale = k_scale;
+  p.q_out = q_out; p.q_out_stride = q_out_stride; p.k_out = k_out; p.k_out_stride = k_out_stride;
+  p.v_out = v_out; p.v_out_stride = v_out_stride; p.k_pool = k_pool; p.v_pool = v_pool; p.block_table = block_table;
+  p.table_width = table_width; p.page_size = page_size; p.num_pages = num_pages; p.positions = positions;
+  p.req_of_token = req_of_token; p.nq = nq; p.nk = nk; p.dim = dim; p.vdim = vdim; p.bad_page = bad_page;
+  const dim3 grid(n_tokens, nq + 2 * nk);
+  if (dtype == YALIS_F32 && out_dtype == YALIS_F32)
+    return yalis_launch(qkv_prepare_kernel<float, float>, grid, dim3(32), 0, stream, p);
+  if (dtype == YALIS_BF16 && out_dtype == YALIS_BF16)
+    return yalis_launch(qkv_prepare_kernel<__nv_bfloat16, __nv_bfloat16>, grid, dim3(32), 0, stream, p);
+  if (dtype == YALIS_BF16 && out_dtype == YALIS_F32)
+    return yalis_launch(qkv_prepare_kernel<__nv_bfloat16, float>, grid, dim3(32), 0, stream, p);
+  return YALIS_ERR_DTYPE;
+}
+
+YALIS_API int yalis_activation(const void* x, int x_stride, void* y, int y_stride, int dtype, int rows, int cols,
+                               int act, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return YALIS_OK;
+  if (act < 0 || act > 2) return YALIS_ERR_SHAPE;
+  const size_t total = (size_t)rows * cols;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  YALIS_DISPATCH_DTYPE(dtype, T,
+                       return yalis_launch(activation_kernel<T>, dim3(blocks), dim3(256), 0, stream, (const T*)x, x_stride,
+                                           (T*)y, y_stride, rows, cols, act));
+  return YALIS_OK;
+}
+
+YALIS_API int yalis_add_rows_vector(float* x, const float* other, const float* vec, int rows, int cols,
+                                    cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return YALIS_OK;
+  const size_t total = (size_t)rows * cols;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  return yalis_launch(add_rows_vector_kernel, dim3(blocks), dim3(256), 0, stream, x, other, vec, rows, cols);
+}

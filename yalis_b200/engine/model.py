@@ -27,6 +27,8 @@ class Model:
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         self.dtype: Optional[torch.dtype] = None
+        self.extra: Dict[str, torch.Tensor] = {}
+        self._keeps_embedding = any(e.before is not None and e.before.embedding for e in spec.schedule)
 
     # ---- tensors ---------------------------------------------------------------------
     def _layer_tensor_names(self, li: int) -> Dict[str, Dict[str, str]]:
@@ -60,6 +62,8 @@ class Model:
                     put(names[slot][local], ps)
         for local, ps in self.final_norm.param_specs().items():
             put(s.final_norm_names[local], ps)
+        for tensor_name, shape in s.extra_tensors.values():
+            put(tensor_name, ParamSpec(tuple(shape), keep_float32=True))
         if s.head_name is not None:
             put(s.head_name, ParamSpec((s.vocab_size, s.hidden_size)))
         return out
@@ -75,6 +79,7 @@ class Model:
                 part.load({local: fetch(name) for local, name in names[slot].items()})
         self.final_norm.load({local: fetch(s.final_norm_names[local]) for local in self.final_norm.param_specs()})
         self.head = self.embedding if s.head_name is None else fetch(s.head_name).contiguous()
+        self.extra = {local: fetch(tensor_name).contiguous() for local, (tensor_name, _) in s.extra_tensors.items()}
 
     # ---- cache -------------------------------------------------------------------------
     def cache_requests(self) -> List[Optional[object]]:
@@ -93,12 +98,21 @@ class Model:
         return tuple(keys)
 
     # ---- forward -----------------------------------------------------------------------
-    def forward(self, ctx, caches: List[Optional[object]]) -> ResidualStream:
+    def forward(self, ctx, caches: List[Optional[object]], tap: Optional[Callable] = None) -> ResidualStream:
+        """``tap(i, x)``, if given, sees the float32 stream [N, hidden] after schedule entry ``i`` (every pending
+        addition applied): for comparisons layer by layer."""
         x = embedding(self.embedding, ctx.token_ids, bad_flag=ctx.error_flag, scale=self.spec.embedding_scale,
                       from_slot=ctx.token_from_slot, chosen=ctx.chosen if ctx.token_from_slot is not None else None)
+        entered = x.clone() if self._keeps_embedding else None
         stream = ResidualStream(x, self.dtype)
-        for entry, cache in zip(self.spec.schedule, caches):
+        for i, (entry, cache) in enumerate(zip(self.spec.schedule, caches)):
+            if entry.before is not None:
+                b = entry.before
+                stream.add_rows(entered if b.embedding else None, self.extra[b.vector][b.row] if b.vector is not None else None)
             self.blocks[entry.layer].forward(stream, ctx, cache)
+            if tap is not None:
+                stream.flush()
+                tap(i, stream.x)
         return stream
 
     def logits(self, stream: ResidualStream, rows: torch.Tensor) -> torch.Tensor:
@@ -110,20 +124,32 @@ class Model:
         return out
 
     def weight_bytes(self) -> int:
-        seen, total = set(), 0
+        """Bytes of every tensor on the device that the model's parts hold (each counted once)."""
+        seen, visited, total = set(), set(), 0
 
-        def add(t):
+        def walk(obj, depth=0):
             nonlocal total
-            if t is not None and t.data_ptr() not in seen:
-                seen.add(t.data_ptr())
-                total += t.numel() * t.element_size()
+            if isinstance(obj, torch.Tensor):
+                if obj.is_cuda and obj.untyped_storage().data_ptr() not in seen:
+                    seen.add(obj.untyped_storage().data_ptr())
+                    total += obj.untyped_storage().nbytes()
+                return
+            if depth > 6 or id(obj) in visited:
+                return
+            if isinstance(obj, (list, tuple)):
+                for v in obj:
+                    walk(v, depth + 1)
+            elif isinstance(obj, dict):
+                for v in obj.values():
+                    walk(v, depth + 1)
+            elif hasattr(obj, "spec") and hasattr(obj, "__dict__"):      # a part
+                visited.add(id(obj))
+                for v in vars(obj).values():
+                    walk(v, depth + 1)
 
-        add(self.embedding)
-        add(self.head)
-        for b in self.blocks:
-            for part in b.parts.values():
-                for v in vars(part).values():
-                    if isinstance(v, torch.Tensor) and v.is_cuda:
-                        add(v)
-        add(getattr(self.final_norm, "weight", None))
+        walk(self.embedding)
+        walk(self.head)
+        walk(self.extra)
+        walk(self.blocks)
+        walk(self.final_norm)
         return total

@@ -33,7 +33,8 @@ class Replayer:
         self.graphs = graphs
         self.steps_replayed = 0        # steps that ran from a recording
         self.engine = engine or Engine(model_dir, dtype=dtype, page_size=page_size,
-                                       num_pages=pool_tokens // page_size, max_slots=max_live)
+                                       num_pages=pool_tokens // page_size, max_slots=max_live,
+                                       max_context=pool_tokens)       # no request can hold more than the pool
 
     def run_step(self, step: Dict) -> Optional[np.ndarray]:
         entries: List[StepEntry] = []

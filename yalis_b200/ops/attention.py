@@ -16,14 +16,17 @@ from yalis_b200 import native
 from ._lib import check, dtype_code, f32, i32, i64, lib, need, need_cuda, ptr, stream
 
 
-def _check_common(name, q, k_pool, v_pool, positions, req_of_token, block_table, num_heads, num_kv_heads, head_dim):
+def _check_common(name, q, k_pool, v_pool, positions, req_of_token, block_table, num_heads, num_kv_heads, head_dim,
+                  v_head_dim=None):
     need_cuda(name, q, k_pool, v_pool, positions, req_of_token, block_table)
     n = q.shape[0]
+    v_head_dim = head_dim if v_head_dim is None else v_head_dim
     need(q.dim() == 2 and q.stride(1) == 1 and q.shape[1] >= num_heads * head_dim, name,
          "q must be [N, >= heads*head_dim] with unit inner stride")
-    need(k_pool.shape == v_pool.shape and k_pool.dim() == 4 and k_pool.shape[1] == num_kv_heads
-         and k_pool.shape[3] == head_dim and k_pool.is_contiguous() and v_pool.is_contiguous(), name,
-         "pools must be contiguous [pages, kv_heads, page_size, head_dim]")
+    need(k_pool.dim() == 4 and v_pool.dim() == 4 and k_pool.shape[:3] == v_pool.shape[:3]
+         and k_pool.shape[1] == num_kv_heads and k_pool.shape[3] == head_dim and v_pool.shape[3] == v_head_dim
+         and k_pool.is_contiguous() and v_pool.is_contiguous(), name,
+         "pools must be contiguous [pages, kv_heads, page_size, head_dim] (values: their own head size)")
     need(k_pool.dtype == q.dtype == v_pool.dtype, name, "q and the pools must have one dtype")
     need(num_heads % num_kv_heads == 0, name, "heads must be a multiple of kv_heads")
     for t in (positions, req_of_token):
@@ -35,28 +38,36 @@ def _check_common(name, q, k_pool, v_pool, positions, req_of_token, block_table,
 def paged_attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, positions: torch.Tensor,
                             req_of_token: torch.Tensor, block_table: torch.Tensor, num_heads: int,
                             num_kv_heads: int, head_dim: int, scale: Optional[float] = None,
-                            window: Optional[int] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                            window: Optional[int] = None, out: Optional[torch.Tensor] = None,
+                            v_head_dim: Optional[int] = None, softcap: Optional[float] = None, sink: bool = False,
+                            out_scale: float = 1.0) -> torch.Tensor:
     """Exact attention of every token over the cached keys of its request.
 
     ``q`` may be the fused qkv matrix (only its first heads*head_dim columns are
     read).  Token t of request r at position p sees keys j of r with
-    p - window < j <= p.  Returns [N, heads*head_dim] in q's dtype.
+    p - window < j <= p.  ``softcap`` c turns a score s into c * tanh(s / c); ``sink``
+    adds 1 to the softmax's denominator (a key of score 0 that has no value);
+    ``v_head_dim`` is the head size of the values when it is not the keys'.  The result,
+    times ``out_scale``, is [N, heads*v_head_dim] in q's dtype (``out`` may be a
+    column block of a wider matrix).
     """
     name = "paged_attention_generic"
     LAUNCHED["generic"] += 1
-    _check_common(name, q, k_pool, v_pool, positions, req_of_token, block_table, num_heads, num_kv_heads, head_dim)
-    need(head_dim % 2 == 0 and head_dim <= 256, name, f"head_dim {head_dim} must be even and at most 256")
+    vd = head_dim if v_head_dim is None else int(v_head_dim)
+    _check_common(name, q, k_pool, v_pool, positions, req_of_token, block_table, num_heads, num_kv_heads, head_dim, vd)
+    need(head_dim <= 256 and vd <= 256, name, f"head sizes {head_dim}, {vd} must be at most 256")
     n = q.shape[0]
     if out is None:
-        out = torch.empty((n, num_heads * head_dim), dtype=q.dtype, device=q.device)
-    need(out.shape == (n, num_heads * head_dim) and out.dtype == q.dtype and out.is_contiguous(), name, "bad out tensor")
+        out = torch.empty((n, num_heads * vd), dtype=q.dtype, device=q.device)
+    need(out.shape == (n, num_heads * vd) and out.dtype == q.dtype and out.stride(1) == 1, name, "bad out tensor")
+    need(softcap is None or softcap > 0, name, "the soft cap must be positive")
     if scale is None:
         scale = 1.0 / math.sqrt(head_dim)
     check(lib().yalis_paged_attention_generic(
         ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(k_pool), ptr(v_pool), i32(dtype_code(q.dtype)),
         ptr(positions), ptr(req_of_token), ptr(block_table), i32(block_table.shape[1]), i32(k_pool.shape[2]),
-        i32(k_pool.shape[0]), i32(n), i32(num_heads), i32(num_kv_heads), i32(head_dim), f32(scale),
-        i32(window or 0), stream()), name)
+        i32(k_pool.shape[0]), i32(n), i32(num_heads), i32(num_kv_heads), i32(head_dim), i32(vd), f32(scale),
+        i32(window or 0), f32(softcap or 0.0), i32(int(sink)), f32(out_scale), stream()), name)
     return out
 
 

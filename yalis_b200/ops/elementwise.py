@@ -164,3 +164,101 @@ def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
     out = torch.empty((rows.numel(), x.shape[1]), dtype=torch.float32, device=x.device)
     check(lib().yalis_gather_rows_f32(ptr(x), ptr(rows), ptr(out), i32(rows.numel()), i32(x.shape[1]), stream()), name)
     return out
+
+
+ACT_GELU_ERF, ACT_GELU_TANH, ACT_SILU = 0, 1, 2
+ACTIVATIONS = {"gelu": ACT_GELU_ERF, "gelu_erf": ACT_GELU_ERF, "gelu_tanh": ACT_GELU_TANH, "silu": ACT_SILU}
+
+
+def activation(x: torch.Tensor, kind: str, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """act(x) element by element in float32: ``gelu_erf`` 0.5 z (1 + erf(z / sqrt 2)), ``gelu_tanh``
+    0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))) or ``silu``.  ``x`` and ``out`` are [N, C] with unit inner
+    stride (column blocks of wider matrices are fine)."""
+    name = "activation"
+    need_cuda(name, x, out)
+    need(kind in ACTIVATIONS, name, f"unknown activation {kind!r} (one of {', '.join(ACTIVATIONS)})")
+    need(x.dim() == 2 and x.stride(1) == 1, name, "x must be [N, C] with unit inner stride")
+    if out is None:
+        out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    need(out.shape == x.shape and out.dtype == x.dtype and out.stride(1) == 1, name, "bad out tensor")
+    check(lib().yalis_activation(ptr(x), i32(x.stride(0)), ptr(out), i32(out.stride(0)), i32(dtype_code(x.dtype)),
+                                 i32(x.shape[0]), i32(x.shape[1]), i32(ACTIVATIONS[kind]), stream()), name)
+    return out
+
+
+def add_rows_vector(x: torch.Tensor, other: Optional[torch.Tensor] = None, vec: Optional[torch.Tensor] = None) -> None:
+    """x[n, :] += other[n, :] + vec[:] in place, float32 (either addend may be absent)."""
+    name = "add_rows_vector"
+    need_cuda(name, x, other, vec)
+    need(x.dtype == torch.float32 and x.dim() == 2 and x.is_contiguous(), name, "x must be contiguous float32 [N, width]")
+    if other is not None:
+        need(other.dtype == torch.float32 and other.shape == x.shape and other.is_contiguous(), name, "other must match x")
+    if vec is not None:
+        need(vec.dtype == torch.float32 and vec.shape == (x.shape[1],) and vec.is_contiguous(), name, "vec must be float32 [width]")
+    check(lib().yalis_add_rows_vector(ptr(x), ptr(other), ptr(vec), i32(x.shape[0]), i32(x.shape[1]), stream()), name)
+
+
+def qkv_prepare(src: torch.Tensor, offsets, nq: int, nk: int, dim: int, vdim: int, positions: torch.Tensor,
+                req_of_token: torch.Tensor, *, out_dtype: torch.dtype, biases=(None, None, None),
+                q_norm: Optional[torch.Tensor] = None, k_norm: Optional[torch.Tensor] = None, norm_eps: float = 0.0,
+                inv_freq: Optional[torch.Tensor] = None, q_scale: float = 1.0, k_scale: float = 1.0,
+                k_pool: Optional[torch.Tensor] = None, v_pool: Optional[torch.Tensor] = None,
+                block_table: Optional[torch.Tensor] = None, store: bool = True,
+                bad_flag: Optional[torch.Tensor] = None):
+    """Prepares the heads of a mixer from its input projection ``src`` [N, ...] (model dtype), whose query,
+    key and value heads start at the columns ``offsets`` = (q, k, v):
+
+        x <- x + bias;  q, k <- x / sqrt(mean(x^2) + norm_eps) * norm (where a norm is given);
+        q, k <- rotation of their first 2 * len(inv_freq) sizes by the angle position * inv_freq (size i paired
+        with i + len(inv_freq)), the other sizes unchanged;  q <- q * q_scale, k <- k * k_scale.
+
+    With pools, keys [pages, nk, page_size, dim] and values [pages, nk, page_size, vdim] are written to the pages
+    of ``block_table`` (not at all when ``store`` is False) and the queries [N, nq * dim] are returned.  Without
+    pools (q, k, v) are returned as plain matrices in ``out_dtype``."""
+    name = "qkv_prepare"
+    need_cuda(name, src, positions, req_of_token, q_norm, k_norm, inv_freq, k_pool, v_pool, block_table, bad_flag, *biases)
+    need(src.dim() == 2 and src.stride(1) == 1, name, "src must be [N, ...] with unit inner stride")
+    n = src.shape[0]
+    q_off, k_off, v_off = (int(o) for o in offsets)
+    need(max(q_off + nq * dim, k_off + nk * dim, v_off + nk * vdim) <= src.shape[1], name, "head columns lie outside src")
+    for t in (positions, req_of_token):
+        need(t.dtype == torch.int32 and t.shape == (n,) and t.is_contiguous(), name, "positions/req_of_token: int32 [N]")
+    for b, width in zip(biases, (nq * dim, nk * dim, nk * vdim)):
+        need(b is None or (b.dtype == src.dtype and b.shape == (width,) and b.is_contiguous()), name,
+             "a bias must be a contiguous vector over its heads in the dtype of src")
+    for w in (q_norm, k_norm):
+        need(w is None or (w.dtype == torch.float32 and w.shape == (dim,) and w.is_contiguous()), name,
+             "a norm scale must be float32 [dim]")
+    rot_dims = 0
+    if inv_freq is not None:
+        need(inv_freq.dtype == torch.float32 and inv_freq.dim() == 1 and inv_freq.is_contiguous()
+             and 2 * inv_freq.numel() <= dim, name, "inv_freq must be float32 [rot_dims / 2], rot_dims <= dim")
+        rot_dims = 2 * inv_freq.numel()
+    paged = k_pool is not None
+    q_out = torch.empty((n, nq * dim), dtype=out_dtype, device=src.device)
+    k_out = v_out = None
+    page_size = num_pages = table_width = 0
+    if paged:
+        need(out_dtype == src.dtype, name, "with pools the queries keep the dtype of src")
+        need(v_pool is not None and block_table is not None and k_pool.dtype == v_pool.dtype == src.dtype
+             and k_pool.dim() == 4 and v_pool.dim() == 4 and k_pool.shape[:3] == v_pool.shape[:3]
+             and k_pool.shape[1] == nk and k_pool.shape[3] == dim and v_pool.shape[3] == vdim
+             and k_pool.is_contiguous() and v_pool.is_contiguous(), name,
+             "pools must be contiguous [pages, kv_heads, page_size, dim] and [..., vdim] in the dtype of src")
+        need(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous(), name,
+             "block_table must be contiguous int32 [R, width]")
+        num_pages, page_size, table_width = k_pool.shape[0], k_pool.shape[2], block_table.shape[1]
+    else:
+        k_out = torch.empty((n, nk * dim), dtype=out_dtype, device=src.device)
+        v_out = torch.empty((n, nk * vdim), dtype=out_dtype, device=src.device)
+    # (with pools but ``store`` False - a layer that reads another entry's cache - the blocks of the key and
+    # value heads find no destination and return)
+    check(lib().yalis_qkv_prepare(
+        ptr(src), i32(dtype_code(src.dtype)), i32(src.stride(0)), i32(q_off), i32(k_off), i32(v_off),
+        ptr(biases[0]), ptr(biases[1]), ptr(biases[2]), ptr(q_norm), ptr(k_norm), f32(norm_eps), ptr(inv_freq),
+        i32(rot_dims), f32(q_scale), f32(k_scale), ptr(q_out), i32(q_out.stride(0)), ptr(k_out),
+        i32(k_out.stride(0) if k_out is not None else 0), ptr(v_out), i32(v_out.stride(0) if v_out is not None else 0),
+        i32(dtype_code(out_dtype)), ptr(k_pool if store else None), ptr(v_pool if store else None), ptr(block_table),
+        i32(table_width), i32(page_size), i32(num_pages), ptr(positions), ptr(req_of_token), i32(n), i32(nq), i32(nk),
+        i32(dim), i32(vdim), ptr(bad_flag), stream()), name)
+    return q_out if paged else (q_out, k_out, v_out)

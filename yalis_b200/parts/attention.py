@@ -18,7 +18,8 @@ import torch
 from yalis_b200.config.spec import PartSpec
 from yalis_b200.ops import attention as attn_ops
 from yalis_b200.ops.linear import linear_partial
-from .base import NOT_ROTARY, Mixer, PagedKV, PagedKVCache, ParamSpec, PositionEncoding, register_part
+from yalis_b200.ops.elementwise import qkv_prepare
+from .base import NOT_ROTARY, Mixer, PagedKV, PagedKVCache, ParamSpec, PositionEncoding, Projected, register_part
 
 
 class PagedAttention(Mixer):
@@ -95,4 +96,95 @@ class PagedAttention(Mixer):
         return linear_partial(y, self.w_o)             # the residual stream adds the partial sums
 
 
+class GeneralAttention(Mixer, Projected):
+    """Grouped-query causal attention over the paged cache with the variations that the fast kernels of
+    ``paged_attention`` do not take.  Parameters: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``
+    (of q and k), ``v_head_dim`` (None: head_dim), ``bias`` (q, k, v = W x + b), ``qk_norm_eps`` (None: no norm;
+    else q and k of every head become x / sqrt(mean(x^2) + eps) * scale before the rotation, one learned scale
+    [head_dim] for q and one for k), ``rotary`` ({"dims", "theta"}: the first ``dims`` sizes of a head turn; None:
+    no rotation), ``scale`` (None: 1/sqrt(head_dim)), ``softcap`` (c: scores become c tanh(s / c)), ``sink`` (1 is
+    added to the softmax's denominator), ``window``, ``out_scale``.  Scores, weights and the weighted sum are
+    float32 in every dtype."""
+
+    def __init__(self, spec: PartSpec, position: Optional[PositionEncoding] = None):
+        if position is None:
+            from .recurrent import position_part
+            position = position_part(spec.params)
+        super().__init__(spec, position)
+        p = spec.params
+        self.hidden, self.nh, self.g, self.hs = int(p["hidden_size"]), int(p["num_heads"]), int(p["num_kv_heads"]), int(p["head_dim"])
+        self.vd = int(p["v_head_dim"]) if p.get("v_head_dim") is not None else self.hs
+        self.bias = bool(p.get("bias", False))
+        self.norm_eps = float(p["qk_norm_eps"]) if p.get("qk_norm_eps") is not None else None
+        self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.hs)
+        self.softcap = float(p["softcap"]) if p.get("softcap") is not None else None
+        self.sink = bool(p.get("sink", False))
+        self.window = p.get("window")
+        self.out_scale = float(p.get("out_scale", 1.0))
+        if self.nh % self.g:
+            raise ValueError(f"num_heads {self.nh} is not a multiple of num_kv_heads {self.g}")
+        if max(self.hs, self.vd) > 256:
+            raise ValueError(f"head sizes {self.hs}, {self.vd} are not supported (at most 256)")
+        self.hidden_width = self.nh * self.vd
+        self.w_in: Optional[torch.Tensor] = None
+        self.w_out: Optional[torch.Tensor] = None
+        self.biases = (None, None, None)
+        self.q_norm = self.k_norm = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        specs = {"q_proj": ParamSpec((self.nh * self.hs, self.hidden)), "k_proj": ParamSpec((self.g * self.hs, self.hidden)),
+                 "v_proj": ParamSpec((self.g * self.vd, self.hidden)), "o_proj": ParamSpec((self.hidden, self.nh * self.vd))}
+        if self.bias:
+            specs.update({"q_bias": ParamSpec((self.nh * self.hs,), init="zeros"), "k_bias": ParamSpec((self.g * self.hs,), init="zeros"),
+                          "v_bias": ParamSpec((self.g * self.vd,), init="zeros")})
+        if self.norm_eps is not None:
+            specs.update({"q_norm": ParamSpec((self.hs,), init="ones", keep_float32=True),
+                          "k_norm": ParamSpec((self.hs,), init="ones", keep_float32=True)})
+        return specs
+
+    def load(self, t: Dict[str, torch.Tensor]) -> None:
+        self.w_in = torch.cat([t["q_proj"], t["k_proj"], t["v_proj"]], dim=0).contiguous()
+        self.w_out = t["o_proj"].contiguous()
+        if self.bias:
+            self.biases = tuple(t[n].to(self.w_in.dtype).contiguous() for n in ("q_bias", "k_bias", "v_bias"))
+        if self.norm_eps is not None:
+            self.q_norm, self.k_norm = t["q_norm"].contiguous(), t["k_norm"].contiguous()
+
+    def in_weight(self) -> torch.Tensor:
+        return self.w_in
+
+    def out_weight(self) -> torch.Tensor:
+        return self.w_out
+
+    def release_projections(self) -> None:
+        self.w_in = self.w_out = None
+
+    def cache_request(self) -> PagedKV:
+        return PagedKV(self.g, self.hs, self.window, v_head_dim=None if self.vd == self.hs else self.vd)
+
+    def capture_key(self, host):
+        return None      # one kernel for every step: a block per token and head, its loop bounds read on the device
+
+    def mixing_flops(self, q_len: int, ctx_before: int) -> float:
+        keys = sum(min(ctx_before + t + 1, self.window or (ctx_before + t + 1)) for t in range(q_len)) if self.window \
+            else q_len * ctx_before + q_len * (q_len + 1) / 2
+        return 2.0 * self.nh * (self.hs + self.vd) * keys
+
+    def mix(self, z: torch.Tensor, ctx, cache: PagedKVCache, y: torch.Tensor) -> None:
+        qd, kd = self.nh * self.hs, self.g * self.hs
+        freq = self.position.rotary_frequencies(self.position.head_dim, z.device) if self.position is not None else None
+        table = ctx.block_tables[cache.group]
+        q = qkv_prepare(z, (0, qd, qd + kd), self.nh, self.g, self.hs, self.vd, ctx.positions, ctx.req_of_token,
+                        out_dtype=z.dtype, biases=self.biases, q_norm=self.q_norm, k_norm=self.k_norm,
+                        norm_eps=self.norm_eps or 0.0, inv_freq=freq, k_pool=cache.k, v_pool=cache.v, block_table=table,
+                        store=cache.writable, bad_flag=ctx.error_flag)
+        attn_ops.paged_attention_generic(q, cache.k, cache.v, ctx.positions, ctx.req_of_token, table, self.nh, self.g, self.hs,
+                                         scale=self.scale, window=self.window, out=y, v_head_dim=self.vd,
+                                         softcap=self.softcap, sink=self.sink, out_scale=self.out_scale)
+
+    def forward(self, x: torch.Tensor, ctx, cache: PagedKVCache) -> torch.Tensor:
+        return self.project_and_mix(x, ctx, cache)
+
+
 register_part("mixer", "paged_attention", PagedAttention)
+register_part("mixer", "general_attention", GeneralAttention)

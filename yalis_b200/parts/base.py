@@ -72,6 +72,11 @@ class PagedKV:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None      # head size of the values when it is not the keys'
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 
 @dataclass(frozen=True)
@@ -80,6 +85,19 @@ class SlotState:
 
     shape: Tuple[int, ...]
     dtype: torch.dtype = torch.float32
+
+
+def cache_leaves(request):
+    """A part that keeps several things (keys in pages and a state, say) asks for them as a dictionary
+    name -> request, nested as deep as its own parts are; the storage answers with the same dictionary of caches.
+    This yields the ``PagedKV`` and ``SlotState`` requests of such a tree (or of a single request)."""
+    if request is None:
+        return
+    if isinstance(request, Mapping):
+        for sub in request.values():
+            yield from cache_leaves(sub)
+    else:
+        yield request
 
 
 class PagedKVCache:
@@ -131,6 +149,12 @@ class ResidualStream:
             from yalis_b200.ops.elementwise import residual_add
             residual_add(self.x, self.pending)
             self.pending = None
+
+    def add_rows(self, other: Optional[torch.Tensor] = None, vector: Optional[torch.Tensor] = None) -> None:
+        """x[n, :] += other[n, :] + vector[:] (float32; either may be absent), after what is pending."""
+        from yalis_b200.ops.elementwise import add_rows_vector
+        self.flush()
+        add_rows_vector(self.x, other, vector)
 
 
 # ---- parts ---------------------------------------------------------------------------
@@ -221,6 +245,59 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class Projected:
+    """What a mixer or feed-forward of the form  W_out core(W_in x)  can say about itself, so that an arrangement
+    in which several of them read one input and add into one sum (a parallel block, mixers side by side) runs
+    ONE product for all their inputs and ONE for all their outputs (the output matrices side by side along K):
+
+    ``in_weight()``    the input matrix [rows, hidden] (after ``load``);
+    ``hidden_width``   columns of the core's result;
+    ``out_weight()``   the output matrix [hidden, hidden_width];
+    ``mix(z, ctx, cache, y)``  the core: reads its rows ``z`` [N, rows] of the input product and writes
+                       ``y`` [N, hidden_width]; both may be column blocks of wider matrices.  A factor on the
+                       part's result is applied to ``y``.
+    ``release_projections()``  the arrangement has copied both matrices into its own: drop them.
+    """
+
+    hidden_width = 0
+
+    def in_weight(self) -> torch.Tensor:
+        raise NotImplementedError
+
+    def out_weight(self) -> torch.Tensor:
+        raise NotImplementedError
+
+    def mix(self, z: torch.Tensor, ctx, cache, y: torch.Tensor) -> None:
+        raise NotImplementedError
+
+    def release_projections(self) -> None:
+        raise NotImplementedError
+
+    def project_and_mix(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
+        """The part on its own: W_out core(W_in x), the last product as partial sums where the kernel splits K."""
+        from yalis_b200.ops.linear import linear, linear_partial
+        z = linear(x, self.in_weight())
+        y = torch.empty((x.shape[0], self.hidden_width), dtype=x.dtype, device=x.device)
+        self.mix(z, ctx, cache, y)
+        return linear_partial(y, self.out_weight())
+
+
+def stack_rows(blocks, multiple: int = 8):
+    """The matrices [rows_i, K] stacked into one, each starting at a row that is a multiple of ``multiple`` (zero rows
+    between them), so that each block of the product's columns starts on a 16-byte boundary.  Returns the matrix and
+    the (start, stop) of every block."""
+    spans, rows, at = [], [], 0
+    for w in blocks:
+        pad = (-at) % multiple
+        if pad:
+            rows.append(torch.zeros((pad, w.shape[1]), dtype=w.dtype, device=w.device))
+            at += pad
+        rows.append(w)
+        spans.append((at, at + w.shape[0]))
+        at += w.shape[0]
+    return torch.cat(rows, dim=0).contiguous(), spans
+
+
 class Block(Part):
     """An arrangement of parts around the residual stream.
 
@@ -233,6 +310,7 @@ class Block(Part):
 
     category = "block"
     slots: Mapping[str, str] = {}
+    optional: Tuple[str, ...] = ()      # places a layer may leave empty
 
     def __init__(self, spec: PartSpec, parts: Dict[str, Part]):
         super().__init__(spec)
@@ -268,7 +346,9 @@ def build_block(layer) -> Block:
         known = ", ".join(sorted(_REGISTRY["block"])) or "none"
         raise ValueError(f"no block of kind {layer.block.kind!r} is registered (known: {known})") from None
     slots = dict(getattr(factory, "slots", {}))
-    missing = [n for n in slots if n not in layer.parts]
+    optional = tuple(getattr(factory, "optional", ()))
+    missing = [n for n in slots if n not in layer.parts and n not in optional]
+    slots = {n: c for n, c in slots.items() if n in layer.parts or n not in optional}
     unknown = [n for n in layer.parts if n not in slots]
     if missing or unknown:
         raise ValueError(f"block kind {layer.block.kind!r} has the places {sorted(slots)}: "
@@ -318,4 +398,4 @@ def registered(category: str) -> Tuple[str, ...]:
 
 
 def _ensure_builtin() -> None:
-    from yalis_b200.parts import attention, block, norm, rotary, swiglu  # noqa: F401
+    from yalis_b200.parts import attention, block, dense, norm, recurrent, rotary, swiglu  # noqa: F401

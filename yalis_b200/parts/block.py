@@ -2,7 +2,12 @@
 
 from __future__ import annotations
 
-from .base import Block, ResidualStream, register_part
+from typing import Optional
+
+import torch
+
+from yalis_b200.ops.linear import linear, linear_partial
+from .base import Block, Projected, ResidualStream, register_part, stack_rows
 
 
 class PreNormResidualBlock(Block):
@@ -20,4 +25,56 @@ class PreNormResidualBlock(Block):
         stream.add(self.feed_forward.forward(h, ctx))
 
 
+class ParallelResidualBlock(Block):
+    """h = norm_1(x);  x += mixer(h) + feed_forward(h): one norm, both sub-layers read its output (the parallel
+    branch of yalis/external/model.py:414-438).  A layer may have no feed-forward.
+
+    When mixer and feed-forward are both of the form W_out core(W_in h) (``Projected``), their input matrices are
+    stacked and their output matrices laid side by side when the weights are loaded, so a layer runs two products:
+    z = h [W_in_mixer; W_in_ff]^T, and after the cores have written their results next to each other,
+    [y_mixer, y_ff] [W_out_mixer, W_out_ff]^T, which is the sum of both sub-layers."""
+
+    slots = {"norm_1": "norm", "mixer": "mixer", "feed_forward": "feed_forward"}
+    optional = ("feed_forward",)
+
+    def __init__(self, spec, parts):
+        super().__init__(spec, parts)
+        self.ff = self.parts.get("feed_forward")
+        self.w_in: Optional[torch.Tensor] = None
+        self.w_out: Optional[torch.Tensor] = None
+        self.spans = []
+
+    def _fuse(self) -> bool:
+        """Stack the matrices of mixer and feed-forward once (the parts have their weights by the first step)."""
+        if self.w_in is not None:
+            return True
+        shared = [p for p in (self.mixer, self.ff) if p is not None]
+        if len(shared) < 2 or not all(isinstance(p, Projected) for p in shared):
+            return False
+        if any(p.in_weight().dtype != shared[0].in_weight().dtype or p.out_weight().dtype != shared[0].out_weight().dtype
+               for p in shared):
+            return False
+        self.w_in, self.spans = stack_rows([p.in_weight() for p in shared])
+        self.w_out = torch.cat([p.out_weight() for p in shared], dim=1).contiguous()
+        for p in shared:
+            p.release_projections()
+        return True
+
+    def forward(self, stream: ResidualStream, ctx, cache) -> None:
+        h = self.norm_1.forward(stream)
+        if self._fuse():
+            z = linear(h, self.w_in)
+            km = self.mixer.hidden_width
+            y = torch.empty((h.shape[0], km + self.ff.hidden_width), dtype=h.dtype, device=h.device)
+            (a, b), (c, d) = self.spans
+            self.mixer.mix(z[:, a:b], ctx, cache, y[:, :km])
+            self.ff.mix(z[:, c:d], ctx, None, y[:, km:])
+            stream.add(linear_partial(y, self.w_out))
+            return
+        stream.add(self.mixer.forward(h, ctx, cache))
+        if self.ff is not None:
+            stream.add(self.ff.forward(h, ctx))
+
+
 register_part("block", "pre_norm_residual", PreNormResidualBlock)
+register_part("block", "parallel_residual", ParallelResidualBlock)

@@ -13,19 +13,22 @@ from .base import Norm, ParamSpec, ResidualStream, register_part
 
 
 class RMSNorm(Norm):
-    """Parameters: ``size`` (width of the stream), ``eps``.  The scale is held in float32."""
+    """Parameters: ``size`` (width of the stream), ``eps``, ``one_plus`` (the stored tensor w lies around
+    zero and the scale is 1 + w; default False: the tensor is the scale).  The scale is held in float32."""
 
     def __init__(self, spec: PartSpec):
         super().__init__(spec)
         self.size = int(spec.params["size"])
         self.eps = float(spec.params["eps"])
+        self.one_plus = bool(spec.params.get("one_plus", False))
         self.weight: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec((self.size,), init="ones", keep_float32=True)}
+        return {"weight": ParamSpec((self.size,), init="zeros" if self.one_plus else "ones", keep_float32=True)}
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.weight = tensors["weight"].contiguous()
+        w = tensors["weight"].contiguous()
+        self.weight = (1.0 + w) if self.one_plus else w       # float32: the sum is exact to one rounding
 
     def forward(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         y = add_rmsnorm(stream.x, stream.pending, self.weight, self.eps, stream.dtype, rows=rows)

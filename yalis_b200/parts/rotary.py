@@ -17,10 +17,15 @@ from yalis_b200.ops.elementwise import rope_kv_write
 from .base import PagedKVCache, PositionEncoding, register_part
 
 
-def inverse_frequencies(head_dim: int, theta: float, scaling: Optional[dict]) -> torch.Tensor:
+def inverse_frequencies(head_dim: int, theta: float, scaling: Optional[dict], exact_powers: bool = False) -> torch.Tensor:
     """theta_i = base^(-2i/hs); with ``scaling``: s = clamp((orig/wavelen - low)/(high - low), 0, 1),
-    theta_i <- (1 - s) * theta_i / factor + s * theta_i.  float32 [head_dim / 2] on the CPU."""
-    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.int64).float() / head_dim))
+    theta_i <- (1 - s) * theta_i / factor + s * theta_i.  float32 [head_dim / 2] on the CPU.
+    ``exact_powers``: the powers are taken in float64 and rounded once (the default takes them in float32, as
+    the reference's table does)."""
+    if exact_powers:
+        inv = torch.tensor([float(theta) ** (-2.0 * i / head_dim) for i in range(head_dim // 2)], dtype=torch.float64).float()
+    else:
+        inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.int64).float() / head_dim))
     if scaling is not None:
         wavelen = 2 * torch.pi / inv
         ratio = scaling["original_max_position_embeddings"] / wavelen
@@ -31,14 +36,16 @@ def inverse_frequencies(head_dim: int, theta: float, scaling: Optional[dict]) ->
 
 
 class RotaryEncoding(PositionEncoding):
-    """Parameters: ``head_dim``, ``theta``, ``scaling`` (None or the four llama3 numbers)."""
+    """Parameters: ``head_dim`` (the sizes that turn: size i is paired with i + head_dim / 2), ``theta``,
+    ``scaling`` (None or the four llama3 numbers), ``exact_powers`` (see ``inverse_frequencies``)."""
 
     def __init__(self, spec: PartSpec):
         super().__init__(spec)
         self.head_dim = int(spec.params["head_dim"])
         if self.head_dim % 2:
             raise ValueError(f"rotary encoding needs an even head_dim, got {self.head_dim}")
-        self.inv_freq_host = inverse_frequencies(self.head_dim, float(spec.params["theta"]), spec.params.get("scaling"))
+        self.inv_freq_host = inverse_frequencies(self.head_dim, float(spec.params["theta"]), spec.params.get("scaling"),
+                                                 bool(spec.params.get("exact_powers", False)))
         self.inv_freq: Optional[torch.Tensor] = None
 
     def load(self, tensors) -> None:
