@@ -1,0 +1,501 @@
+"""Tirezen on the GPU against the plain implementation: every mechanism's kernel alone, then whole models cut
+into steps in every way, then generation through the entry point.
+
+Kernel tests build their own index arrays (which token belongs to which request, where a request's portion
+starts, which slot it holds) and compare with the functions of ``plain_tirezen`` in float64.  Model tests make
+small model folders of three configurations that differ in every size and option and replay requests whole,
+with a decoded tail, in portions down to two tokens, and mixed with few pages and slots.
+"""
+
+import math
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_tirezen as plain
+import traces
+from tirezen_models import tirezen_dir, write_model
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def i32(values):
+    return torch.tensor(list(values), dtype=torch.int32, device=DEV)
+
+
+def step_arrays(portions):
+    """portions: list of (slot, start position, count) -> req_of_token, q_start, slots, positions."""
+    req, pos, qs, slots = [], [], [0], []
+    for r, (slot, start, count) in enumerate(portions):
+        req += [r] * count
+        pos += list(range(start, start + count))
+        qs.append(qs[-1] + count)
+        slots.append(slot)
+    return i32(req), i32(qs), i32(slots), i32(pos)
+
+
+def cuts(total, sizes):
+    out, at, i = [], 0, 0
+    while at < total:
+        c = min(sizes[i % len(sizes)], total - at)
+        out.append((at, c))
+        at += c
+        i += 1
+    return out
+
+
+# ---- the short convolution -----------------------------------------------------------------------------
+
+@pytest.mark.parametrize("taps, channels, dtype", [(4, 70, torch.float32), (2, 33, torch.bfloat16), (5, 8, torch.float32), (1, 5, torch.float32)])
+def test_short_conv_continues_from_the_tail_in_its_slot(taps, channels, dtype):
+    from yalis_b200.ops.recurrent import short_conv_silu
+    g = torch.Generator().manual_seed(taps)
+    lengths = {0: 23, 2: 9, 3: 1}                       # slot -> tokens of the request that holds it
+    xs = {s: torch.randn(n, channels, generator=g).to(dtype) for s, n in lengths.items()}
+    w = torch.randn(channels, taps, generator=g)
+    want = {s: plain.silu(plain.short_conv(x.double(), w.double())) for s, x in xs.items()}
+    rows = torch.zeros(5, 16 + channels * (taps - 1) + 3, device=DEV)
+    rows.fill_(7.0)                                      # what an earlier request left behind
+    for s in lengths:
+        rows[s].zero_()                                  # admission zeroes the slot
+    got = {s: [] for s in lengths}
+    at = {s: 0 for s in lengths}
+    sizes = {0: [1, 2, 7, 1, 3], 2: [2, 2, 5], 3: [1]}
+    step = 0
+    while any(at[s] < lengths[s] for s in lengths):
+        portions, parts = [], []
+        for s in lengths:
+            if at[s] < lengths[s]:
+                c = min(sizes[s][step % len(sizes[s])], lengths[s] - at[s])
+                portions.append((s, at[s], c))
+                parts.append(xs[s][at[s]:at[s] + c])
+                at[s] += c
+        req, qs, slots, _ = step_arrays(portions)
+        wide = torch.cat([torch.zeros(sum(p[2] for p in portions), 8, dtype=dtype), torch.cat(parts)], dim=1).to(DEV)
+        out = short_conv_silu(wide[:, 8:], w.to(DEV), rows, 16, req, qs, slots)      # a column block of a wider matrix
+        o = 0
+        for s, _, c in portions:
+            got[s].append(out[o:o + c].cpu())
+            o += c
+        step += 1
+    for s in lengths:
+        torch.testing.assert_close(torch.cat(got[s]).double(), want[s], rtol=1e-5, atol=1e-5)
+    assert float(rows[1, 0]) == 7.0 and float(rows[0, 0]) == 0.0      # other slots and the state before the tail untouched
+
+
+# ---- the recurrences ------------------------------------------------------------------------------------------
+
+def plain_scan(q, k, v, mode, heads, kv_heads, decay=None, a_raw=None, a_log=None, dt_bias=None, b_raw=None, normalize=False):
+    T = q.shape[0]
+    D, V = q.shape[1] // kv_heads, v.shape[1] // heads
+    q, k, v = q.double().reshape(T, kv_heads, D), k.double().reshape(T, kv_heads, D), v.double().reshape(T, heads, V)
+    if normalize:
+        q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * D ** -0.5
+        k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+    q, k = q.repeat_interleave(heads // kv_heads, 1), k.repeat_interleave(heads // kv_heads, 1)
+    if mode == "retention":
+        out = torch.zeros(T, heads, V, dtype=torch.float64)
+        for h in range(heads):
+            S = torch.zeros(D, V, dtype=torch.float64)
+            for t in range(T):
+                S = float(decay[h]) * S + torch.outer(k[t, h], v[t, h])
+                out[t, h] = S.T @ q[t, h]
+        return out.reshape(T, -1)
+    a = a_raw.double() + dt_bias.double()
+    if mode == "head":
+        g = torch.exp(-torch.exp(a_log.double()) * plain.softplus(a))
+    else:
+        g = torch.exp(-torch.exp(a_log.double())[None, :, None] * plain.softplus(a).reshape(T, heads, D))
+    return plain.delta_rule(q, k, v, torch.sigmoid(b_raw.double()), g).reshape(T, -1)
+
+
+@pytest.mark.parametrize("mode, heads, kv_heads, D, V, raw_dtype", [
+    ("retention", 2, 2, 16, 24, torch.float32), ("retention", 1, 1, 40, 8, torch.float32),
+    ("head", 4, 2, 12, 20, torch.float32), ("head", 3, 3, 6, 10, torch.bfloat16), ("head", 2, 1, 128, 64, torch.float32),
+    ("channel", 4, 2, 8, 16, torch.float32), ("channel", 2, 1, 20, 6, torch.bfloat16), ("channel", 2, 2, 64, 130, torch.float32),
+    ("head", 1, 1, 200, 32, torch.float32),
+])
+def test_state_scan_against_the_plain_recurrence_however_the_tokens_are_cut(mode, heads, kv_heads, D, V, raw_dtype):
+    from yalis_b200.ops.recurrent import StateLayout, state_scan
+    g = torch.Generator().manual_seed(D * 7 + V)
+    lay = StateLayout(heads, D, V, conv_channels=3, taps=3)
+    lengths = [37, 5, 64]
+    data = []
+    for T in lengths:
+        d = {"q": torch.randn(T, kv_heads * D, generator=g), "k": torch.randn(T, kv_heads * D, generator=g),
+             "v": torch.randn(T, heads * V, generator=g)}
+        if mode == "retention":
+            d["q"], d["k"] = d["q"] / D ** 0.5, d["k"] / D ** 0.5
+        else:
+            d["a_raw"] = torch.randn(T, heads if mode == "head" else heads * D, generator=g).to(raw_dtype)
+            d["b_raw"] = torch.randn(T, heads, generator=g).to(raw_dtype)
+        data.append(d)
+    consts = {}
+    if mode == "retention":
+        consts["decay"] = torch.tensor([0.9, 0.99][:heads])
+    else:
+        consts["a_log"] = torch.rand(heads, generator=g) - 1.0
+        consts["dt_bias"] = torch.randn(heads if mode == "head" else heads * D, generator=g)
+    want = [plain_scan(d["q"], d["k"], d["v"], mode, heads, kv_heads, normalize=mode != "retention",
+                       **{k: d[k] for k in ("a_raw", "b_raw") if k in d}, **consts) for d in data]
+
+    def run(plan, rows):
+        """plan: list of steps, each a list of (request, start, count); slots = request index + 1."""
+        got = [torch.zeros(T, heads * V, dtype=torch.float64) for T in lengths]
+        for step in plan:
+            _, qs, slots, _ = step_arrays([(r + 1, a, c) for r, a, c in step])
+            cat = {key: torch.cat([data[r][key][a:a + c] for r, a, c in step]).to(DEV) for key in data[0]}
+            kw = {k: v.to(DEV) for k, v in consts.items()}
+            if mode != "retention":
+                kw.update(a_raw=cat["a_raw"], b_raw=cat["b_raw"], normalize=True, q_scale=D ** -0.5)
+            out = state_scan(cat["q"], cat["k"], cat["v"], rows, lay, qs, slots, kv_heads=kv_heads, delta=mode != "retention", **kw)
+            o = 0
+            for r, a, c in step:
+                got[r][a:a + c] = out[o:o + c].double().cpu()
+                o += c
+        return got
+
+    def fresh():
+        rows = torch.zeros(5, lay.total, device=DEV)
+        rows[0].fill_(3.0)
+        rows[4].fill_(-2.0)
+        return rows
+
+    whole = run([[(r, 0, T)] for r, T in enumerate(lengths)], fresh())
+    for r in range(3):
+        scale = want[r].abs().max()
+        assert float((whole[r] - want[r]).abs().max() / scale) < (3e-5 if raw_dtype == torch.float32 else 3e-5), (mode, r)
+    # all three together in one step, and cut into portions of 1, 2, 3, 16 and 17 tokens with requests coming and going
+    together = run([[(r, 0, T) for r, T in enumerate(lengths)]], fresh())
+    pieces = {r: cuts(T, s) for (r, T), s in zip(enumerate(lengths), ([2, 1, 17, 3], [1, 2], [16, 1, 2, 30]))}
+    plan = []
+    for i in range(max(len(p) for p in pieces.values())):
+        step = [(r, *pieces[r][i]) for r in pieces if i < len(pieces[r])]
+        plan.append(step[::-1] if i % 2 else step)
+    rows = fresh()
+    cut = run(plan, rows)
+    for r in range(3):
+        assert torch.equal(together[r], whole[r]) and torch.equal(cut[r], whole[r]), (mode, r)    # the same bits
+    assert float(rows[0, 0]) == 3.0 and float(rows[4, 5]) == -2.0                                # nobody else's slot
+    assert float(rows[1, lay.state_floats:].abs().sum()) == 0                                    # the tail behind the state
+
+
+def test_a_far_token_stays_readable_in_a_slowly_decaying_state():
+    """One early token writes a large value under a key that only the last query asks for."""
+    from yalis_b200.ops.recurrent import StateLayout, state_scan
+    T, D, V = 700, 16, 8
+    g = torch.Generator().manual_seed(1)
+    k = torch.randn(T, D, generator=g) * 0.1
+    q = torch.randn(T, D, generator=g) * 0.1
+    v = torch.randn(T, V, generator=g) * 0.1
+    k[5], v[5] = 0.0, 0.0
+    k[5, 3], v[5] = 4.0, torch.arange(V, dtype=torch.float32) + 1.0
+    q[-1] = 0.0
+    q[-1, 3] = 2.0
+    lay = StateLayout(1, D, V)
+    rows = torch.zeros(2, lay.total, device=DEV)
+    _, qs, slots, _ = step_arrays([(0, 0, T - 1)])
+    decay = torch.tensor([0.999], device=DEV)
+    state_scan(q[:-1].to(DEV), k[:-1].to(DEV), v[:-1].to(DEV), rows, lay, qs, slots, kv_heads=1, delta=False, decay=decay)
+    _, qs, slots, _ = step_arrays([(0, T - 1, 1)])
+    out = state_scan(q[-1:].to(DEV), k[-1:].to(DEV), v[-1:].to(DEV), rows, lay, qs, slots, kv_heads=1, delta=False, decay=decay)
+    want = plain_scan(q, k, v, "retention", 1, 1, decay=[0.999])[-1]
+    assert float(want.abs().max()) > 3.0                         # the far token dominates the answer
+    torch.testing.assert_close(out[0].double().cpu(), want, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype, gate_kind, weighted", [(torch.float32, 1, True), (torch.bfloat16, 2, True), (torch.float32, 0, False)])
+def test_head_norm_gate(dtype, gate_kind, weighted):
+    from yalis_b200.ops.recurrent import head_norm_gate
+    g = torch.Generator().manual_seed(3)
+    N, H, V, eps = 9, 3, 20, 1e-3
+    o = torch.randn(N, H * V, generator=g) * 0.05
+    gate = torch.randn(N, H * V, generator=g).to(dtype)
+    w = 1 + 0.3 * torch.randn(V, generator=g)
+    req = i32([0] * 4 + [-1] + [1] * 4)
+    wide = torch.full((N, H * V + 5), 9.0, dtype=dtype, device=DEV)
+    head_norm_gate(o.to(DEV), H, V, eps, req, wide[:, 5:], weight=w.to(DEV) if weighted else None,
+                   gate=gate.to(DEV) if gate_kind else None, gate_kind=gate_kind, out_scale=0.5)
+    want = plain.rms(o.double().reshape(N, H, V), eps)
+    if weighted:
+        want = want * w.double()
+    want = want.reshape(N, H * V)
+    if gate_kind == 1:
+        want = want * plain.silu(gate.double())
+    if gate_kind == 2:
+        want = want * torch.sigmoid(gate.double())
+    got = wide[:, 5:].double().cpu()
+    keep = [i for i in range(N) if i != 4]
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    torch.testing.assert_close(got[keep], 0.5 * want[keep], rtol=tol, atol=tol)
+    assert float(wide[4, 5:].float().mean()) == 9.0 and float(wide[:, :5].float().mean()) == 9.0     # padding row and other columns
+
+
+# ---- heads prepared for attention and the attention itself -------------------------------------------------------
+
+def test_heads_are_biased_normed_partly_rotated_and_stored():
+    from yalis_b200.ops.elementwise import qkv_prepare
+    g = torch.Generator().manual_seed(5)
+    nq, nk, D, V, rot, page = 4, 2, 16, 8, 12, 4
+    portions = [(0, 6, 5), (1, 0, 3)]                      # a request at positions 6..10 and a fresh one
+    req, qs, slots, pos = step_arrays(portions)
+    N = 8
+    src = torch.randn(N, 3 + nq * D + nk * D + nk * V, generator=g)
+    bias = [torch.randn(n, generator=g) for n in (nq * D, nk * D, nk * V)]
+    qn, kn = 1 + 0.3 * torch.randn(D, generator=g), 1 + 0.3 * torch.randn(D, generator=g)
+    inv = torch.tensor([50.0 ** (-2.0 * i / rot) for i in range(rot // 2)], dtype=torch.float32)
+    k_pool = torch.zeros(6, nk, page, D, device=DEV)
+    v_pool = torch.zeros(6, nk, page, V, device=DEV)
+    table = i32([3, 5, 0, 1, 2, 4, -1, -1]).reshape(2, 4)
+    q = qkv_prepare(src.to(DEV), (3, 3 + nq * D, 3 + nq * D + nk * D), nq, nk, D, V, pos, req, out_dtype=torch.float32,
+                    biases=tuple(b.to(DEV) for b in bias), q_norm=qn.to(DEV), k_norm=kn.to(DEV), norm_eps=1e-4,
+                    inv_freq=inv.to(DEV), k_pool=k_pool, v_pool=v_pool, block_table=table)
+    s = src.double()
+    for n in range(N):
+        p = int(pos[n])
+        for name, heads, off, b, w in (("q", nq, 3, bias[0], qn), ("k", nk, 3 + nq * D, bias[1], kn)):
+            x = (s[n, off:off + heads * D] + b.double()).reshape(1, heads, D)
+            x = plain.rms(x, 1e-4) * w.double()
+            full = torch.zeros(p + 1, heads, D, dtype=torch.float64)
+            full[p] = x[0]
+            want = plain.rotate(full, {"dims": rot, "base": 50.0})[p]
+            if name == "q":
+                got = q[n].double().cpu().reshape(heads, D)
+            else:
+                pg = int(table[int(req[n]), p // page])
+                got = k_pool[pg, :, p % page].double().cpu()
+            torch.testing.assert_close(got, want, rtol=2e-5, atol=2e-5)
+                torch.testing.assert_close(got[:, rot:], x[0, :, rot:], rtol=1e-5, atol=1e-5)      # past rot.dims: unchanged
+        pg = int(table[int(req[n]), p // page])
+        want_v = (s[n, 3 + nq * D + nk * D:] + bias[2].double()).reshape(nk, V)
+        torch.testing.assert_close(v_pool[pg, :, p % page].double().cpu(), want_v, rtol=1e-6, atol=1e-6)
+
+
+def plain_attention(q, k, v, scale, cap, sink):
+    """q [H, D] at the last position over k [T, G, D], v [T, G, V]."""
+    H, G = q.shape[0], k.shape[1]
+    out = torch.zeros(H, v.shape[2], dtype=torch.float64)
+    for h in range(H):
+        s = (k[:, h // (H // G)] @ q[h]) * scale
+        if cap:
+            s = cap * torch.tanh(s / cap)
+        e = torch.exp(s - (0 if sink else s.max()))
+        out[h] = (e / ((1.0 if sink else 0.0) + e.sum())) @ v[:, h // (H // G)]
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_with_cap_sink_and_value_size_sees_a_far_key_across_pages(dtype):
+    from yalis_b200.ops.attention import paged_attention_generic
+    g = torch.Generator().manual_seed(11)
+    H, G, D, V, page, T = 4, 2, 16, 40, 16, 600
+    k = (torch.randn(T, G, D, generator=g) * 0.3).to(dtype)
+    v = torch.randn(T, G, V, generator=g).to(dtype)
+    q = (torch.randn(3, H, D, generator=g) * 0.3).to(dtype)       # queries at positions T-3, T-2, T-1
+    k[15] *= 0                                                    # the last key of the first page: one score stands out
+    k[15, :, 2] = 6.0
+    q[2, :, 2] = 5.0
+    v[15] = 3.0
+    n_pages = -(-T // page)
+    perm = torch.randperm(n_pages + 3, generator=g)[:n_pages]
+    k_pool = torch.zeros(n_pages + 3, G, page, D, dtype=dtype, device=DEV)
+    v_pool = torch.zeros(n_pages + 3, G, page, V, dtype=dtype, device=DEV)
+    for t in range(T):
+        k_pool[perm[t // page], :, t % page] = k[t].to(DEV)
+        v_pool[perm[t // page], :, t % page] = v[t].to(DEV)
+    table = perm.to(torch.int32).reshape(1, -1).to(DEV)
+    req, pos = i32([0, 0, 0]), i32([T - 3, T - 2, T - 1])
+    for cap, sink, scale in ((4.0, True, 0.5), (None, True, 0.25), (2.0, False, 0.5), (None, False, 0.25)):
+        out = paged_attention_generic(q.reshape(3, H * D).to(DEV), k_pool, v_pool, pos, req, table, H, G, D, scale=scale,
+                                      v_head_dim=V, softcap=cap, sink=sink, out_scale=1.5)
+        for j in range(3):
+            want = 1.5 * plain_attention(q[j].double(), k[:T - 2 + j].double(), v[:T - 2 + j].double(), scale, cap, sink)
+            tol = 1e-5 if dtype == torch.float32 else 2e-2
+            torch.testing.assert_close(out[j].double().cpu().reshape(H, V), want, rtol=tol, atol=tol)
+        if cap is None:
+            assert float(out[2].float().mean()) > 1.5 * 2.0      # uncapped, the far key takes most of the weight
+    # scores far below zero: the sink takes the weight and the answer goes to zero instead of to a mean of values
+    low = -q.abs() * 8
+    out = paged_attention_generic(low.reshape(3, H * D).to(DEV), k_pool.abs(), v_pool, pos, req, table, H, G, D,
+                                  scale=4.0, v_head_dim=V, sink=True)
+    with_sink = plain_attention(low[2].double(), k.abs().double(), v.double(), 4.0, None, True)
+    without = plain_attention(low[2].double(), k.abs().double(), v.double(), 4.0, None, False)
+    assert float(with_sink.abs().max()) < 0.05 < 0.3 < float(without.abs().max())
+    torch.testing.assert_close(out[2].double().cpu().reshape(H, V), with_sink, rtol=2e-2, atol=2e-3)
+
+
+def test_activation_and_row_additions():
+    from yalis_b200.ops.elementwise import activation, add_rows_vector
+    g = torch.Generator().manual_seed(2)
+    z = torch.randn(7, 33, generator=g) * 3
+    wide = torch.zeros(7, 40, device=DEV)
+    activation(z.to(DEV), "gelu_erf", out=wide[:, 4:37])
+    torch.testing.assert_close(wide[:, 4:37].double().cpu(), plain.gelu_erf(z.double()), rtol=1e-6, atol=1e-6)
+    tanh_form = 0.5 * z.double() * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z.double() + 0.044715 * z.double() ** 3)))
+    torch.testing.assert_close(activation(z.to(DEV), "gelu_tanh").double().cpu(), tanh_form, rtol=1e-6, atol=1e-6)
+    assert float((plain.gelu_erf(z.double()) - tanh_form).abs().max()) > 1e-4       # the two forms are told apart
+    x = torch.randn(5, 12, generator=g)
+    e, vec = torch.randn(5, 12, generator=g), torch.randn(12, generator=g)
+    xd = x.to(DEV)
+    add_rows_vector(xd, e.to(DEV), vec.to(DEV))
+    torch.testing.assert_close(xd.cpu(), x + e + vec)
+    add_rows_vector(xd, None, vec.to(DEV))
+    torch.testing.assert_close(xd.cpu(), x + e + 2 * vec)
+
+
+# ---- whole models -----------------------------------------------------------------------------------------------------
+
+TOL = {"float32": 1e-4, "bfloat16": 4e-2}       # relative to the largest |logit| of the request
+LENGTHS = {"A": [1, 5, 33, 70, 21, 48], "B": [2, 40, 9, 64, 17, 90], "C": [3, 37, 18, 65, 12, 30]}
+PAGE = {"A": 16, "B": 8, "C": 64}
+_oracle = {}
+
+
+def requests_for(which):
+    cfg = plain.read_config(tirezen_dir(which))
+    g = torch.Generator().manual_seed(ord(which))
+    return {f"r{i}": torch.randint(0, cfg["vocab"], (n,), generator=g).tolist() for i, n in enumerate(LENGTHS[which])}
+
+
+def oracle(which):
+    if which not in _oracle:
+        d = tirezen_dir(which)
+        cfg, w = plain.read_config(d), plain.read_weights(d, torch.float64)
+        _oracle[which] = {rid: plain.forward(t, w, cfg).numpy() for rid, t in requests_for(which).items()}
+    return _oracle[which]
+
+
+def replay(which, dtype, steps, max_tokens):
+    from yalis_b200.engine.replay import Replayer
+    rep = Replayer(tirezen_dir(which), dtype, max_tokens, page_size=PAGE[which])
+    out = {}
+    for s in steps:
+        r = rep.run_step(s)
+        if r is not None:
+            out[s["step"]] = r
+    rep.engine.manager.check()
+    for grp in rep.engine.groups:
+        assert rep.engine.manager.free_pages(grp.name) == grp.num_pages          # every page came back
+    return out, rep
+
+
+def compare(got, want, tol, what):
+    assert set(got) == set(want), what
+    for rid in want:
+        assert got[rid].shape == want[rid].shape, (what, rid)
+        scale = np.abs(want[rid]).max()
+        err = np.abs(got[rid] - want[rid]).max(axis=1) / scale
+        if err.max() > tol:
+            raise AssertionError(f"{what}: request {rid} differs by {err.max():.3e} (tolerance {tol}); first wrong "
+                                 f"position {int(np.argmax(err > tol))} of {len(err)}")
+
+
+@pytest.mark.parametrize("which", ["A", "B", "C"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_requests_cut_four_ways_agree_with_the_plain_model(which, dtype):
+    reqs, want = requests_for(which), oracle(which)
+    vocab = plain.read_config(tirezen_dir(which))["vocab"]
+    results = {}
+    for name, steps in (("whole", traces.whole(reqs)), ("tail", traces.tail_decoded(reqs, tail=12)),
+                        ("portions", traces.portions(reqs, seed=3)), ("mixed", traces.mixed(reqs, seed=5, tail=6))):
+        steps = traces.number(steps)
+        out, rep = replay(which, dtype, steps, traces.peak_tokens(steps, max(64, PAGE[which])))
+        got = traces.collect(steps, out, vocab)
+        compare(got, want, TOL[dtype], f"{which} {dtype} {name}")
+        results[name] = got
+    # how a request was cut, what ran beside it and which pages and slots it had leave (nearly) no trace
+    for name in ("tail", "portions", "mixed"):
+        for rid in want:
+            scale = np.abs(want[rid]).max()
+            assert np.abs(results[name][rid] - results["whole"][rid]).max() / scale < (2e-5 if dtype == "float32" else 2e-2), (name, rid)
+
+
+def test_the_residual_stream_after_every_layer_run():
+    """Float32, one request: the stream after each of the seven layer runs of configuration A."""
+    from yalis_b200.engine.engine import Engine, StepEntry
+    d = tirezen_dir("A")
+    cfg, w = plain.read_config(d), plain.read_weights(d, torch.float64)
+    tokens = requests_for("A")["r2"]
+    want = []
+    plain.forward(tokens, w, cfg, want)
+    eng = Engine(d, dtype="float32", page_size=16, num_pages=8, max_slots=2, max_context=128)
+    eng.add_request("x")
+    seen = []
+    slots = [eng.slot_of("x")]
+    inner = eng.model.forward
+    eng.model.forward = lambda ctx, caches: inner(ctx, caches, tap=lambda i, x: seen.append(x.double().cpu()))
+    eng.run([StepEntry("x", tokens, [len(tokens) - 1])])
+    assert len(seen) == len(want) == 7
+    for i, (a, b) in enumerate(zip(seen, want)):
+        assert float((a - b).abs().max() / b.abs().max()) < 2e-5, f"layer run {i}"
+
+
+def test_long_decoding_keeps_to_the_plain_model():
+    """300 tokens one by one after a two-token prompt, float32: the state is carried 300 times."""
+    from yalis_b200.engine.engine import Engine, StepEntry
+    d = tirezen_dir("B")
+    cfg, w = plain.read_config(d), plain.read_weights(d, torch.float64)
+    g = torch.Generator().manual_seed(9)
+    tokens = torch.randint(0, cfg["vocab"], (302,), generator=g).tolist()
+    want = plain.forward(tokens, w, cfg).numpy()
+    eng = Engine(d, dtype="float32", page_size=8, num_pages=48, max_slots=2, max_context=384)
+    eng.add_request("x")
+    rows = [eng.run([StepEntry("x", tokens[:2], [0, 1])]).logits.cpu().numpy()]
+    for t in tokens[2:]:
+        rows.append(eng.run([StepEntry("x", [t], [0])]).logits.cpu().numpy())
+    got = np.concatenate(rows)
+    eng.check_device_errors()
+    assert np.abs(got - want).max() / np.abs(want).max() < 1e-4
+
+
+def test_a_slot_and_its_pages_used_again_start_clean():
+    from yalis_b200.engine.engine import Engine, StepEntry
+    d = tirezen_dir("C")
+    reqs = requests_for("C")
+    eng = Engine(d, dtype="float32", page_size=64, num_pages=2, max_slots=1, max_context=128)
+    first = None
+    for rid in ("r3", "r1", "r3"):
+        assert eng.add_request(rid) == 0                       # the only slot, every time
+        out = eng.run([StepEntry(rid, reqs[rid], [len(reqs[rid]) - 1])]).logits.cpu().numpy()
+        eng.finish_request(rid)
+        if rid == "r3":
+            if first is None:
+                first = out
+            else:
+                assert np.array_equal(first, out)              # what r1 left in slot and pages does not show
+
+
+@pytest.mark.parametrize("which", ["A", "B"])
+def test_greedy_generation_through_the_entry_point(which):
+    from yalis_b200 import InferenceConfig, LLMEngine, ModelConfig
+    d = tirezen_dir(which)
+    cfg, w = plain.read_config(d), plain.read_weights(d, torch.float64)
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, cfg["vocab"], (n,), generator=g).tolist() for n in (3, 19, 40, 7, 26)]
+    engine = LLMEngine(ModelConfig(model_name=f"tirezen-tiny-{which}", model_path=d, precision="fp32"),
+                       InferenceConfig(max_batch_size=3, max_length_of_generated_sequences=64, temperature=0.0, top_p=0.0,
+                                       page_size=PAGE[which]))
+    tokens, metrics = engine.generate(prompts, tokens_to_generate=10)[:2]
+    for p, row in zip(prompts, tokens.cpu().tolist()):
+        assert row == plain.greedy(p, 10, w, cfg)
+
+
+def test_the_replay_program_runs_a_tirezen_folder(tmp_path):
+    import json
+    import subprocess
+    reqs = {k: v for k, v in requests_for("A").items() if k in ("r1", "r2")}
+    steps = traces.number(traces.portions(reqs, seed=1))
+    out_dir = tmp_path / "out"
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", tirezen_dir("A"), "--dtype", "float32",
+                           "--out", str(out_dir), "--max-tokens", str(traces.peak_tokens(steps))],
+                          input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {s['step']}" for s in steps]
+    vocab = plain.read_config(tirezen_dir("A"))["vocab"]
+    outputs = {s["step"]: np.fromfile(out_dir / f"{s['step']}.f32", dtype="<f4") for s in steps}
+    compare(traces.collect(steps, outputs, vocab), {k: oracle("A")[k] for k in reqs}, TOL["float32"], "program")

@@ -69,6 +69,70 @@ PRESETS["tiny-D"] = dict(
     torch_dtype="bfloat16", bos_token_id=None, eos_token_id=None)
 
 
+
+# ---- Tirezen: layers of three kinds of mixer, some of them run several times -------------------------------
+
+def _retention(heads, dim, vdim, decay, rot_dims, base, ff):
+    return {"type": "retention", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "decay": list(decay),
+                                           "rot": {"dims": rot_dims, "base": base}},
+            "mlp": None if ff is None else {"kind": "dense", "ff": ff}}
+
+
+def _delta(heads, kv_heads, dim, vdim, conv, ff):
+    return {"type": "delta", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv},
+            "mlp": None if ff is None else {"kind": "dense", "ff": ff}}
+
+
+def _parallel(left, right, left_scale, right_scale, ff):
+    lh, lg, ld, lv, rot_dims, base, scale, cap = left
+    rh, rg, rd, rv, conv, decay_rank, gate_rank = right
+    return {"type": "parallel",
+            "mixer": {"left": {"heads": lh, "kv_heads": lg, "dim": ld, "vdim": lv, "rot": {"dims": rot_dims, "base": base},
+                               "scale": scale, "softcap": cap},
+                      "right": {"heads": rh, "kv_heads": rg, "dim": rd, "vdim": rv, "conv": conv,
+                                "decay_rank": decay_rank, "gate_rank": gate_rank},
+                      "left_scale": left_scale, "right_scale": right_scale},
+            "mlp": None if ff is None else {"kind": "dense", "ff": ff}}
+
+
+def _tirezen(width, vocab, layers, loop=None, eps=1e-5) -> Dict[str, Any]:
+    cfg = {"architecture": "Tirezen", "width": width, "vocab": vocab, "norm": {"eps": eps}, "layers": layers}
+    if loop is not None:
+        cfg["loop"] = dict(zip(("start", "stop", "times"), loop))
+    return cfg
+
+
+def _tirezen_stack(width, vocab, groups, heads, dim, kv_heads, ff) -> Dict[str, Any]:
+    """``groups`` times (delta, parallel, retention) at the sizes of a real model: head size ``dim`` everywhere."""
+    layers = []
+    for _ in range(groups):
+        layers.append(_delta(heads, kv_heads, dim, dim, 4, ff))
+        layers.append(_parallel((heads, kv_heads, dim, dim, dim, 10000.0, dim ** -0.5, 30.0),
+                                (heads, kv_heads, dim, dim, 4, 64, 64), 1.0, 1.0, ff))
+        layers.append(_retention(heads, dim, dim, [1.0 - 2.0 ** (-5 - (i % 4)) for i in range(heads)], dim, 10000.0, ff))
+    return _tirezen(width, vocab, layers)
+
+
+# Test shapes.  A: three passes over the first two layers, partial rotation, grouped heads, value sizes that differ
+# from key sizes, a layer without feed-forward.  B: no loop, sizes that are multiples of nothing, one head, one pass.
+# C: state matrices of 64 and 128 rows, a loop in the middle.
+PRESETS["tirezen-tiny-A"] = _tirezen(64, 96, [
+    _retention(2, 16, 24, [0.9, 0.97], 8, 100.0, 48),
+    _parallel((4, 2, 16, 8, 12, 10000.0, 0.3, 5.0), (4, 2, 8, 16, 3, 8, 4), 0.7, 1.3, 80),
+    _delta(4, 2, 12, 20, 2, None)], loop=(0, 2, 3))
+PRESETS["tirezen-tiny-B"] = _tirezen(40, 50, [
+    _delta(3, 3, 6, 10, 5, 24),
+    _parallel((3, 1, 20, 36, 20, 500.0, 0.2, 30.0), (2, 1, 20, 6, 4, 5, 12), 1.0, 0.25, None),
+    _retention(1, 40, 8, [0.99], 16, 1000000.0, 56)], eps=1e-6)
+PRESETS["tirezen-tiny-C"] = _tirezen(128, 160, [
+    _delta(2, 1, 128, 64, 4, 96),
+    _retention(2, 64, 128, [0.96875, 0.9990234375], 64, 10000.0, 96),
+    _parallel((2, 2, 64, 64, 32, 10000.0, 0.125, 20.0), (2, 2, 64, 32, 4, 16, 16), 1.2, 0.5, 96)], loop=(1, 2, 2))
+# Sizes that resemble a real model's layers (random weights, for the benchmark).
+PRESETS["tirezen-1b"] = _tirezen_stack(2048, 32000, 5, 16, 128, 8, 8192)
+PRESETS["tirezen-3b"] = _tirezen_stack(3072, 32000, 8, 24, 128, 8, 8192)
+
+
 def preset(name: str) -> Dict[str, Any]:
     """A fresh copy of the named configuration dictionary."""
     for key in (name, name.split("/")[-1], name.split("/")[-1].replace("Meta-", "")):

@@ -64,7 +64,7 @@ class LLMEngine:
         self.inference_config = ic = inference_config
         if model_config.random_weights:
             cfg = preset(model_config.model_name)
-            ec = ic.engine_config(model_config.precision, min(ic.max_length, cfg["max_position_embeddings"]), device)
+            ec = ic.engine_config(model_config.precision, min(ic.max_length, cfg.get("max_position_embeddings", ic.max_length)), device)
             self.engine = Engine(config=cfg, seed=model_config.seed, engine_config=ec)
         else:
             self.engine = Engine(model_config.model_path, engine_config=ic.engine_config(model_config.precision, None, device))

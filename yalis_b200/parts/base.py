@@ -295,6 +295,8 @@ def stack_rows(blocks, multiple: int = 8):
         rows.append(w)
         spans.append((at, at + w.shape[0]))
         at += w.shape[0]
+    if at % multiple:           # rows of the product start on the boundary too
+        rows.append(torch.zeros(((-at) % multiple, rows[0].shape[1]), dtype=rows[0].dtype, device=rows[0].device))
     return torch.cat(rows, dim=0).contiguous(), spans
 
 
