@@ -5,6 +5,7 @@ Llama-3-8B shape (random weights, bfloat16, page size 16), batch 8, 1,024-token 
     python bench.py [--gpus 1] [--steps K] [--warmup W]        # prints ONE JSON line
     python bench.py --impl reference                            # the reference arm (baseline/reference_arm.py)
     python bench.py --workload mixed-1b | serve-3b              # the other workloads, one JSON line each
+    python bench.py --workload mixers [--sizes 1b,3b]           # Tirezen beside the Llama shape of equal size
 
 A "step" is one decode step of the whole batch.  ``value`` is decoded tokens per second
 with the K steps timed on the device (CUDA events) and the chosen tokens fed back on
@@ -27,6 +28,13 @@ those mixed steps.  ``--workload serve-3b``: Llama-3.2-3B shape, 32 requests wit
 of 128 to 16,384 tokens, 256 new tokens each at temperature 0.8; ``value`` is generated
 tokens per second of the whole call.  For these, ``--warmup`` and ``--steps`` count whole
 calls (defaults 2 and 3; the median call is reported).
+
+``--workload mixers``: for each size, the Tirezen preset (layers of delta rule, attention beside a
+delta rule, and retention) and the Llama preset of the same width: a 2,048-token prefill and decode
+steps at batch 8 and 64 after 1,024-token prompts, each with its fraction of the roofline (prefill:
+matrix and mixing flops over the measured bf16 peak; decode: weights, keys and per-request state
+over the measured copy bandwidth).  ``value`` is Tirezen's decode tokens per second at batch 8 of
+the first size.
 """
 
 from __future__ import annotations
@@ -263,13 +271,77 @@ def run_workload(args) -> int:
     return 0
 
 
+def run_mixers(args) -> int:
+    import gc
+    import torch
+    from yalis_b200 import InferenceConfig, LLMEngine, ModelConfig
+    from yalis_b200.bench_support import DecodeBench, model_numbers, prefill_bench
+    from yalis_b200.ops import _lib
+
+    peaks, peak_source = load_peaks()
+    pairs = {"1b": ("tirezen-1b", "Llama-3.2-1B"), "3b": ("tirezen-3b", "Llama-3.2-3B")}
+    steps = args.steps or 64
+    warm = max(3, args.warmup or 8)
+    batches = (8, 64)
+    out, clocks, launches = {}, None, 0
+    for size in args.sizes.split(","):
+        out[size] = {}
+        for name in pairs[size]:
+            max_len = PROMPT_LEN + steps + warm + 64
+            llm = LLMEngine(ModelConfig(model_name=name, random_weights=True, seed=0, precision="bf16"),
+                            InferenceConfig(max_batch_size=max(batches), max_length_of_generated_sequences=max(max_len, PREFILL_TOKENS + 64),
+                                            temperature=0.0, top_p=0.0, page_size=args.page_size,
+                                            cache_tokens=max(batches) * (max_len + args.page_size),
+                                            max_tokens_per_step=max(PREFILL_TOKENS, 8 * PROMPT_LEN)))
+            engine = llm.engine
+            numbers = model_numbers(engine)
+            pf = prefill_bench(engine, PREFILL_TOKENS, warmup=3, iters=5)
+            flops = numbers["flops_prefill"](PREFILL_TOKENS)
+            rec = {"weights_gb": round(numbers["weight_bytes_per_step"] / 1e9, 3),
+                   "prefill": {"tokens": PREFILL_TOKENS, "ms": round(pf, 3), "tok_s": round(PREFILL_TOKENS / (pf / 1e3), 1),
+                               "frac_of_bf16_peak": round(flops / (pf / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)}}
+            for b in batches:
+                bench = DecodeBench(engine, b, PROMPT_LEN, seed=b)
+                bench.prepare()
+                bench.run(warm)
+                first = name.startswith("tirezen") and b == batches[0] and clocks is None
+                if first:
+                    with ClockSampler() as cs:
+                        ms = bench.run_timed(steps)
+                    clocks, launches = cs.summary(), bench.launches_per_step * steps
+                else:
+                    ms = bench.run_timed(steps)
+                step_bytes = (numbers["weight_bytes_per_step"] + b * bench.mean_context(steps) * numbers["kv_bytes_per_token"]
+                              + b * numbers["state_bytes_per_request"])
+                rec[f"decode_b{b}"] = {"ms_per_step": round(ms / steps, 4), "tok_s": round(b * steps / (ms / 1e3), 1),
+                                       "launches_per_step": bench.launches_per_step,
+                                       "frac_of_hbm_peak": round(step_bytes / (ms / steps / 1e3) / 1e9 / peaks["hbm_gbs"], 4)}
+                bench.finish()
+            out[size][name] = rec
+            del llm, engine, bench
+            gc.collect()
+            torch.cuda.empty_cache()
+    first_size = args.sizes.split(",")[0]
+    main_r = out[first_size][pairs[first_size][0]]["decode_b8"]
+    print(json.dumps({
+        "metric": f"decode tok/s (Tirezen {first_size} shape, batch 8, {PROMPT_LEN}-token prompts)", "value": main_r["tok_s"],
+        "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warm, "ms_per_step": main_r["ms_per_step"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "impl": "ours", "workload": "mixers",
+        "data": "synthetic: uniform random token ids, random weights", "models": out, "clocks": clocks,
+        "gpu_launches": int(launches),
+        "config": {"page_size": args.page_size, "prompt_len": PROMPT_LEN, "prefill_tokens": PREFILL_TOKENS, "peaks": peak_source,
+                   "l2": "inputs larger than L2 (weights of 1.9 GB and more per step)"}}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode-8b", choices=["decode-8b", "mixed-1b", "serve-3b"])
+    ap.add_argument("--workload", default="decode-8b", choices=["decode-8b", "mixed-1b", "serve-3b", "mixers"])
+    ap.add_argument("--sizes", default="1b,3b", help="for --workload mixers: which pairs of models to run")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--page-size", type=int, default=None, help="tokens per cache page (default: 16 as the benchmark "
                     "configuration states for decode-8b, the engine's 64 for the other workloads)")
@@ -285,6 +357,8 @@ def main() -> int:
                               "portions beside decoding requests, nor requests of unequal lengths without padding"}))
             return 0
         args.page_size = args.page_size or 64
+        if args.workload == "mixers":
+            return run_mixers(args)
         return run_workload(args)
     args.steps = 256 if args.steps is None else args.steps
     args.warmup = 16 if args.warmup is None else args.warmup

@@ -90,70 +90,63 @@ def test_short_conv_continues_from_the_tail_in_its_slot(taps, channels, dtype):
 
 # ---- the recurrences ------------------------------------------------------------------------------------------
 
-def plain_scan(q, k, v, mode, heads, kv_heads, decay=None, a_raw=None, a_log=None, dt_bias=None, b_raw=None, normalize=False):
+def plain_scan(q, k, v, heads, kv_heads, decay, beta=None):
+    """q, k [T, kv_heads * D], v [T, heads * V]; decay [heads], [T, heads] or [T, heads * D]; beta [T, heads] or None."""
     T = q.shape[0]
     D, V = q.shape[1] // kv_heads, v.shape[1] // heads
     q, k, v = q.double().reshape(T, kv_heads, D), k.double().reshape(T, kv_heads, D), v.double().reshape(T, heads, V)
-    if normalize:
-        q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * D ** -0.5
-        k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
     q, k = q.repeat_interleave(heads // kv_heads, 1), k.repeat_interleave(heads // kv_heads, 1)
-    if mode == "retention":
-        out = torch.zeros(T, heads, V, dtype=torch.float64)
-        for h in range(heads):
-            S = torch.zeros(D, V, dtype=torch.float64)
-            for t in range(T):
-                S = float(decay[h]) * S + torch.outer(k[t, h], v[t, h])
-                out[t, h] = S.T @ q[t, h]
-        return out.reshape(T, -1)
-    a = a_raw.double() + dt_bias.double()
-    if mode == "head":
-        g = torch.exp(-torch.exp(a_log.double()) * plain.softplus(a))
+    decay = torch.as_tensor(decay, dtype=torch.float64)
+    if decay.dim() == 1:
+        g = decay[None, :].expand(T, heads)
+    elif decay.shape[1] == heads:
+        g = decay
     else:
-        g = torch.exp(-torch.exp(a_log.double())[None, :, None] * plain.softplus(a).reshape(T, heads, D))
-    return plain.delta_rule(q, k, v, torch.sigmoid(b_raw.double()), g).reshape(T, -1)
+        g = decay.reshape(T, heads, D)
+    if beta is not None:
+        return plain.delta_rule(q, k, v, beta.double(), g).reshape(T, -1)
+    out = torch.zeros(T, heads, V, dtype=torch.float64)
+    for h in range(heads):
+        S = torch.zeros(D, V, dtype=torch.float64)
+        for t in range(T):
+            gt = g[t, h]
+            S = S * (gt[:, None] if gt.dim() == 1 else gt) + torch.outer(k[t, h], v[t, h])
+            out[t, h] = S.T @ q[t, h]
+    return out.reshape(T, -1)
 
 
-@pytest.mark.parametrize("mode, heads, kv_heads, D, V, raw_dtype", [
-    ("retention", 2, 2, 16, 24, torch.float32), ("retention", 1, 1, 40, 8, torch.float32),
-    ("head", 4, 2, 12, 20, torch.float32), ("head", 3, 3, 6, 10, torch.bfloat16), ("head", 2, 1, 128, 64, torch.float32),
-    ("channel", 4, 2, 8, 16, torch.float32), ("channel", 2, 1, 20, 6, torch.bfloat16), ("channel", 2, 2, 64, 130, torch.float32),
-    ("head", 1, 1, 200, 32, torch.float32),
+@pytest.mark.parametrize("mode, heads, kv_heads, D, V", [
+    ("retention", 2, 2, 16, 24), ("retention", 1, 1, 40, 8), ("head", 4, 2, 12, 20), ("head", 3, 3, 6, 10),
+    ("head", 2, 1, 128, 64), ("channel", 4, 2, 8, 16), ("channel", 2, 1, 20, 6), ("channel", 2, 2, 64, 130),
+    ("head", 1, 1, 200, 32), ("plain_channel", 2, 2, 10, 12),
 ])
-def test_state_scan_against_the_plain_recurrence_however_the_tokens_are_cut(mode, heads, kv_heads, D, V, raw_dtype):
+def test_state_scan_against_the_plain_recurrence_however_the_tokens_are_cut(mode, heads, kv_heads, D, V):
     from yalis_b200.ops.recurrent import StateLayout, state_scan
     g = torch.Generator().manual_seed(D * 7 + V)
     lay = StateLayout(heads, D, V, conv_channels=3, taps=3)
     lengths = [37, 5, 64]
+    delta = mode in ("head", "channel")
     data = []
     for T in lengths:
-        d = {"q": torch.randn(T, kv_heads * D, generator=g), "k": torch.randn(T, kv_heads * D, generator=g),
+        d = {"q": torch.randn(T, kv_heads * D, generator=g) / D ** 0.5, "k": torch.randn(T, kv_heads * D, generator=g) / D ** 0.5,
              "v": torch.randn(T, heads * V, generator=g)}
-        if mode == "retention":
-            d["q"], d["k"] = d["q"] / D ** 0.5, d["k"] / D ** 0.5
-        else:
-            d["a_raw"] = torch.randn(T, heads if mode == "head" else heads * D, generator=g).to(raw_dtype)
-            d["b_raw"] = torch.randn(T, heads, generator=g).to(raw_dtype)
+        if delta:
+            d["k"] = d["k"] * 1.5                        # keys near unit length: the delta rule's own regime
+            d["beta"] = torch.rand(T, heads, generator=g)
+        if mode != "retention":
+            d["decay"] = torch.rand(T, heads if mode == "head" else heads * D, generator=g) * 0.7 + 0.3
         data.append(d)
-    consts = {}
-    if mode == "retention":
-        consts["decay"] = torch.tensor([0.9, 0.99][:heads])
-    else:
-        consts["a_log"] = torch.rand(heads, generator=g) - 1.0
-        consts["dt_bias"] = torch.randn(heads if mode == "head" else heads * D, generator=g)
-    want = [plain_scan(d["q"], d["k"], d["v"], mode, heads, kv_heads, normalize=mode != "retention",
-                       **{k: d[k] for k in ("a_raw", "b_raw") if k in d}, **consts) for d in data]
+    const_decay = torch.tensor([0.9, 0.99][:heads])
+    want = [plain_scan(d["q"], d["k"], d["v"], heads, kv_heads, d.get("decay", const_decay), d.get("beta")) for d in data]
 
     def run(plan, rows):
         """plan: list of steps, each a list of (request, start, count); slots = request index + 1."""
         got = [torch.zeros(T, heads * V, dtype=torch.float64) for T in lengths]
         for step in plan:
             _, qs, slots, _ = step_arrays([(r + 1, a, c) for r, a, c in step])
-            cat = {key: torch.cat([data[r][key][a:a + c] for r, a, c in step]).to(DEV) for key in data[0]}
-            kw = {k: v.to(DEV) for k, v in consts.items()}
-            if mode != "retention":
-                kw.update(a_raw=cat["a_raw"], b_raw=cat["b_raw"], normalize=True, q_scale=D ** -0.5)
-            out = state_scan(cat["q"], cat["k"], cat["v"], rows, lay, qs, slots, kv_heads=kv_heads, delta=mode != "retention", **kw)
+            cat = {key: torch.cat([data[r][key][a:a + c] for r, a, c in step]).to(DEV).contiguous() for key in data[0]}
+            out = state_scan(cat["q"], cat["k"], cat["v"], rows, lay, qs, slots, kv_heads=kv_heads,
+                             decay=cat.get("decay", const_decay.to(DEV)), beta=cat.get("beta"))
             o = 0
             for r, a, c in step:
                 got[r][a:a + c] = out[o:o + c].double().cpu()
@@ -169,7 +162,7 @@ def test_state_scan_against_the_plain_recurrence_however_the_tokens_are_cut(mode
     whole = run([[(r, 0, T)] for r, T in enumerate(lengths)], fresh())
     for r in range(3):
         scale = want[r].abs().max()
-        assert float((whole[r] - want[r]).abs().max() / scale) < (3e-5 if raw_dtype == torch.float32 else 3e-5), (mode, r)
+        assert float((whole[r] - want[r]).abs().max() / scale) < 3e-5, (mode, r)
     # all three together in one step, and cut into portions of 1, 2, 3, 16 and 17 tokens with requests coming and going
     together = run([[(r, 0, T) for r, T in enumerate(lengths)]], fresh())
     pieces = {r: cuts(T, s) for (r, T), s in zip(enumerate(lengths), ([2, 1, 17, 3], [1, 2], [16, 1, 2, 30]))}
@@ -183,6 +176,35 @@ def test_state_scan_against_the_plain_recurrence_however_the_tokens_are_cut(mode
         assert torch.equal(together[r], whole[r]) and torch.equal(cut[r], whole[r]), (mode, r)    # the same bits
     assert float(rows[0, 0]) == 3.0 and float(rows[4, 5]) == -2.0                                # nobody else's slot
     assert float(rows[1, lay.state_floats:].abs().sum()) == 0                                    # the tail behind the state
+
+
+@pytest.mark.parametrize("dtype, per_channel", [(torch.float32, False), (torch.bfloat16, True)])
+def test_delta_rule_inputs_unit_length_decay_and_write_strength(dtype, per_channel):
+    from yalis_b200.ops.recurrent import delta_prepare
+    g = torch.Generator().manual_seed(21)
+    G, H, D, V, taps = 2, 4, 12, 5, 3
+    C = 2 * G * D + H * V
+    portions = [(1, 0, 6), (0, 0, 2)]
+    req, qs, slots, _ = step_arrays(portions)
+    x = torch.randn(8, C, generator=g).to(dtype)
+    w = torch.randn(C, taps, generator=g)
+    a_raw = torch.randn(8, H * D if per_channel else H, generator=g).to(dtype)
+    b_raw = torch.randn(8, H, generator=g).to(dtype)
+    a_log, dt_bias = torch.rand(H, generator=g) - 0.5, torch.randn(a_raw.shape[1], generator=g)
+    rows = torch.zeros(3, C * (taps - 1) + 2, device=DEV)
+    out, decay, beta = delta_prepare(x.to(DEV), w.to(DEV), rows, 0, req, qs, slots, unit_heads=G, dim=D, q_scale=D ** -0.5,
+                                     a_raw=a_raw.to(DEV), a_log=a_log.to(DEV), dt_bias=dt_bias.to(DEV), b_raw=b_raw.to(DEV))
+    for a, n in ((0, 6), (6, 2)):
+        y = plain.silu(plain.short_conv(x[a:a + n].double(), w.double()))
+        q, k = y[:, :G * D].reshape(n, G, D), y[:, G * D:2 * G * D].reshape(n, G, D)
+        q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * D ** -0.5
+        k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+        want = torch.cat([q.reshape(n, -1), k.reshape(n, -1), y[:, 2 * G * D:]], dim=1)
+        torch.testing.assert_close(out[a:a + n].double().cpu(), want, rtol=1e-5, atol=1e-6)
+    e = torch.exp(a_log.double())
+    e = e.repeat_interleave(D) if per_channel else e
+    torch.testing.assert_close(decay.double().cpu(), torch.exp(-e * plain.softplus(a_raw.double() + dt_bias.double())), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(beta.double().cpu(), torch.sigmoid(b_raw.double()), rtol=1e-5, atol=1e-6)
 
 
 def test_a_far_token_stays_readable_in_a_slowly_decaying_state():
@@ -201,10 +223,10 @@ def test_a_far_token_stays_readable_in_a_slowly_decaying_state():
     rows = torch.zeros(2, lay.total, device=DEV)
     _, qs, slots, _ = step_arrays([(0, 0, T - 1)])
     decay = torch.tensor([0.999], device=DEV)
-    state_scan(q[:-1].to(DEV), k[:-1].to(DEV), v[:-1].to(DEV), rows, lay, qs, slots, kv_heads=1, delta=False, decay=decay)
+    state_scan(q[:-1].to(DEV), k[:-1].to(DEV), v[:-1].to(DEV), rows, lay, qs, slots, kv_heads=1, decay=decay)
     _, qs, slots, _ = step_arrays([(0, T - 1, 1)])
-    out = state_scan(q[-1:].to(DEV), k[-1:].to(DEV), v[-1:].to(DEV), rows, lay, qs, slots, kv_heads=1, delta=False, decay=decay)
-    want = plain_scan(q, k, v, "retention", 1, 1, decay=[0.999])[-1]
+    out = state_scan(q[-1:].to(DEV), k[-1:].to(DEV), v[-1:].to(DEV), rows, lay, qs, slots, kv_heads=1, decay=decay)
+    want = plain_scan(q, k, v, 1, 1, [0.999])[-1]
     assert float(want.abs().max()) > 3.0                         # the far token dominates the answer
     torch.testing.assert_close(out[0].double().cpu(), want, rtol=1e-4, atol=1e-5)
 
@@ -270,7 +292,7 @@ def test_heads_are_biased_normed_partly_rotated_and_stored():
                 pg = int(table[int(req[n]), p // page])
                 got = k_pool[pg, :, p % page].double().cpu()
             torch.testing.assert_close(got, want, rtol=2e-5, atol=2e-5)
-                torch.testing.assert_close(got[:, rot:], x[0, :, rot:], rtol=1e-5, atol=1e-5)      # past rot.dims: unchanged
+            torch.testing.assert_close(got[:, rot:], x[0, :, rot:], rtol=1e-5, atol=1e-5)      # past rot.dims: unchanged
         pg = int(table[int(req[n]), p // page])
         want_v = (s[n, 3 + nq * D + nk * D:] + bias[2].double()).reshape(nk, V)
         torch.testing.assert_close(v_pool[pg, :, p % page].double().cpu(), want_v, rtol=1e-6, atol=1e-6)

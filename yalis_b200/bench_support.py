@@ -11,7 +11,7 @@ import time
 import torch
 
 from yalis_b200.engine.engine import Engine, StepEntry
-from yalis_b200.parts.base import PagedKV
+from yalis_b200.parts.base import PagedKV, SlotState, cache_leaves
 from yalis_b200.sampling.sampler import GREEDY
 
 
@@ -25,9 +25,18 @@ def model_numbers(engine: Engine) -> Dict[str, object]:
     # embedding table only the rows of the step's tokens are read
     weight_bytes = m.weight_bytes() - (0 if tied else emb_bytes)
     kv_per_token = 0
-    for req, cache in zip(m.cache_requests(), engine.storage.entries):
-        if isinstance(req, PagedKV) and getattr(cache, "writable", False):
-            kv_per_token += 2 * req.num_kv_heads * req.head_dim * elt
+    state_per_request = 0          # bytes of per-request state a decode step reads and writes back
+    for req, entry in zip(m.cache_requests(), engine.spec.schedule):
+        if entry.cache_of is not None:
+            continue
+        for leaf in cache_leaves(req):
+            if isinstance(leaf, PagedKV):
+                kv_per_token += leaf.num_kv_heads * (leaf.head_dim + leaf.value_dim) * elt
+            elif isinstance(leaf, SlotState):
+                n = 1
+                for d in leaf.shape:
+                    n *= d
+                state_per_request += 2 * n * torch.empty((), dtype=leaf.dtype).element_size()
     matrix_flops = 0.0
     mixers = []
     for entry in engine.spec.schedule:
@@ -41,7 +50,7 @@ def model_numbers(engine: Engine) -> Dict[str, object]:
         return tokens * matrix_flops + sum(mx.mixing_flops(tokens, 0) for mx in mixers) + 2.0 * logit_rows * head_params
 
     return {"weight_bytes_per_step": weight_bytes, "kv_bytes_per_token": kv_per_token, "flops_prefill": flops_prefill,
-            "matrix_flops_per_token": matrix_flops}
+            "matrix_flops_per_token": matrix_flops, "state_bytes_per_request": state_per_request}
 
 
 SETTLE_SECONDS = 1.0     # idle time between the prompt phase and the decode steps of DecodeBench

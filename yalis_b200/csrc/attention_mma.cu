@@ -25,6 +25,12 @@
 // its (request, KV head); the block that draws the last ticket merges all splits
 // in index order (so the result does not depend on which block came last) and
 // resets the counter for the next launch.
+//
+// The general form (GEN) adds what some mixers ask of attention: scores squeezed by
+// c * tanh(s / c), a sink (a key of score 0 and no value: 1 more in the denominator), a
+// factor on the result, and weights that meet V with 16 bits of mantissa instead of 8:
+// P is split into its bfloat16 rounding and the bfloat16 rounding of the rest, and both
+// halves go through the tensor cores (the sum of the weights is float32 in either form).
 #include "common.cuh"
 
 namespace {
@@ -47,6 +53,11 @@ struct AttnParams {
   int page_shift;              // log2(page_size) if it is a power of two, else -1
   int nh, g, per;              // per = nh / g
   float scale_log2;            // scale * log2(e)
+  float cap_log2;              // GEN: soft cap * log2(e) (0: no cap)
+  float scale_over_cap;        // GEN: scale / soft cap
+  int sink;                    // GEN: 1 adds exp(0) to every row's denominator
+  float out_scale;             // GEN: factor on the result
+  int exact_weights;           // ask for the general form even without cap, sink or factor
   int window;                  // 0: none
   int n_splits;
   float* part_o;               // [N, nh, n_splits, HS] (split mode)
@@ -125,7 +136,26 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* k_dst, __nv_bfloat16
 }
 
 // DEC: the block has at most 16 rows; warps split the keys of a tile instead of the rows.
-template <int HS, bool DEC>
+// A score in the exp2 domain: s * scale * log2(e), or with a cap c: c * tanh(s * scale / c) * log2(e).
+template <bool GEN>
+__device__ __forceinline__ float score_log2(const AttnParams& p, float s) {
+  if (GEN && p.cap_log2 > 0.f) return p.cap_log2 * tanhf(s * p.scale_over_cap);
+  return s * p.scale_log2;
+}
+
+// Normalisation of a finished row: with a sink the denominator gains exp2(0 - m) for the row's maximum m
+// (the maximum itself is raised to 0 first when all scores lie below it).
+template <bool GEN>
+__device__ __forceinline__ float finish_factor(const AttnParams& p, float m, float l) {
+  if (GEN && p.sink) {
+    // numerator and denominator are relative to exp2(m): the sink is exp2(-m) in that unit
+    l += exp2f(-m);
+    return p.out_scale / l;
+  }
+  return l > 0.f ? (GEN ? p.out_scale : 1.0f) / l : 0.f;
+}
+
+template <int HS, bool DEC, bool GEN>
 __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(const AttnParams p) {
   constexpr int LD = HS + 8;            // padded row: ldmatrix rows fall into distinct banks
   constexpr int KSTEPS = HS / 16;       // k-steps of Q K^T
@@ -255,7 +285,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(const 
       for (int j = 0; j < ST; ++j) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          s[j][e] *= p.scale_log2;
+          s[j][e] = score_log2<GEN>(p, s[j][e]);
           m_new[e >> 1] = fmaxf(m_new[e >> 1], s[j][e]);
         }
       }
@@ -267,7 +297,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(const 
           const int i = e >> 1;
           const int key = key0 + wkey + j * 8 + tig * 2 + (e & 1);
           const bool vis = row_ok[i] && key <= row_pos[i] && (p.window <= 0 || key > row_pos[i] - p.window);
-          const float v = vis ? s[j][e] * p.scale_log2 : -INFINITY;
+          const float v = vis ? score_log2<GEN>(p, s[j][e]) : -INFINITY;
           s[j][e] = v;
           m_new[i] = fmaxf(m_new[i], v);
         }
@@ -286,6 +316,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(const 
       m_run[i] = m_new[i];
     }
     unsigned pf[ST / 2][4];
+    unsigned pr[GEN ? ST / 2 : 1][4];              // GEN: what the bfloat16 rounding of P left over
 #pragma unroll
     for (int j = 0; j < ST; ++j) {
       const float p0 = exp2f(s[j][0] - base[0]), p1 = exp2f(s[j][1] - base[0]);
@@ -294,6 +325,12 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(const 
       l_add[1] += p2 + p3;
       pf[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);
       pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+      if constexpr (GEN) {
+        const float r0 = p0 - __bfloat162float(__float2bfloat16_rn(p0)), r1 = p1 - __bfloat162float(__float2bfloat16_rn(p1));
+        const float r2 = p2 - __bfloat162float(__float2bfloat16_rn(p2)), r3 = p3 - __bfloat162float(__float2bfloat16_rn(p3));
+        pr[j >> 1][(j & 1) * 2 + 0] = pack_bf16(r0, r1);
+        pr[j >> 1][(j & 1) * 2 + 1] = pack_bf16(r2, r3);
+      }
     }
 #pragma unroll
     for (int i = 0; i < 2; ++i) l_run[i] = l_run[i] * corr[i] + l_add[i];
@@ -313,6 +350,10 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(const 
         ldmatrix_x4_trans(vb, vt + key * LD + dim);
         mma_bf16(o[d], pf[kk], vb[0], vb[1]);
         mma_bf16(o[d + 1], pf[kk], vb[2], vb[3]);
+        if constexpr (GEN) {
+          mma_bf16(o[d], pr[kk], vb[0], vb[1]);
+          mma_bf16(o[d + 1], pr[kk], vb[2], vb[3]);
+        }
       }
     }
     cp_async_wait<NST - 2>();   // tile it + 1 has landed (later ones may still fly)
@@ -361,7 +402,13 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(const 
       const int t = row / p.per, h = row - t * p.per;
       const int tok = tok0 + t, head = kvh * p.per + h;
       if (p.n_splits == 1) {
-        p.out[(size_t)tok * p.out_stride + (size_t)head * HS + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+        if (GEN && p.sink) {
+          const float up = fmaxf(mm, 0.f);          // the sink may be the row's largest score
+          acc *= exp2f(mm - up);
+          ll = ll * exp2f(mm - up);
+          mm = up;
+        }
+        p.out[(size_t)tok * p.out_stride + (size_t)head * HS + d] = __float2bfloat16_rn(acc * finish_factor<GEN>(p, mm, ll));
       } else {
         const size_t slot = ((size_t)tok * p.nh + head) * p.n_splits + split;
         p.part_o[slot * HS + d] = acc;
@@ -397,7 +444,13 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(const 
             ll += ml[(base + sp) * 2 + 1] * f;
             acc += po[(base + sp) * HS + d] * f;
           }
-          p.out[(size_t)tok * p.out_stride + (size_t)head * HS + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+          if (GEN && p.sink) {
+            const float up = fmaxf(mm, 0.f);
+            acc *= exp2f(mm - up);
+            ll = ll * exp2f(mm - up);
+            mm = up;
+          }
+          p.out[(size_t)tok * p.out_stride + (size_t)head * HS + d] = __float2bfloat16_rn(acc * finish_factor<GEN>(p, mm, ll));
         }
         if (threadIdx.x == 0) p.tickets[blockIdx.y] = 0;
       }
@@ -409,7 +462,14 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(const 
     const int row = row0 + wrow + gid + i * 8;
     const int t = row / p.per, h = row - t * p.per;
     const int tok = tok0 + t, head = kvh * p.per + h;
-    const float inv = l_run[i] > 0.f ? 1.0f / l_run[i] : 0.f;
+    float inv;
+    if (GEN && p.sink) {
+      const float up = fmaxf(m_run[i], 0.f);
+      const float down = exp2f(m_run[i] - up);       // m_run = -inf (no visible key) gives 0
+      inv = down * finish_factor<GEN>(p, up, l_run[i] * down);
+    } else {
+      inv = finish_factor<GEN>(p, m_run[i], l_run[i]);
+    }
     __nv_bfloat16* dst = p.out + (size_t)tok * p.out_stride + (size_t)head * HS;
 #pragma unroll
     for (int d = 0; d < DT; ++d) {
@@ -420,27 +480,31 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(const 
   }
 }
 
-template <int HS, bool DEC>
+template <int HS, bool DEC, bool GEN>
 int launch_mode(const AttnParams& p, int n_requests, int max_rows, cudaStream_t stream) {
   constexpr int LD = HS + 8;
   constexpr int RB = DEC ? 16 : BM, NST = DEC ? 3 : 2;
   const size_t smem = (size_t)(RB + 2 * NST * BN) * LD * sizeof(__nv_bfloat16);
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(paged_attention_mma_kernel<HS, DEC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(paged_attention_mma_kernel<HS, DEC, GEN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem) != cudaSuccess)
       return YALIS_ERR_LAUNCH;
     configured = true;
   }
   dim3 grid((max_rows + RB - 1) / RB, n_requests * p.g, p.n_splits);
   if (grid.y > 65535 || grid.z > 65535) return YALIS_ERR_SHAPE;
-  return yalis_launch(paged_attention_mma_kernel<HS, DEC>, grid, dim3(NWARPS * 32), smem, stream, p);
+  return yalis_launch(paged_attention_mma_kernel<HS, DEC, GEN>, grid, dim3(NWARPS * 32), smem, stream, p);
 }
 
 template <int HS>
 int launch(const AttnParams& p, int n_requests, int max_rows, cudaStream_t stream) {
-  return max_rows <= 16 ? launch_mode<HS, true>(p, n_requests, max_rows, stream)
-                        : launch_mode<HS, false>(p, n_requests, max_rows, stream);
+  const bool general = p.cap_log2 > 0.f || p.sink || p.out_scale != 1.0f || p.exact_weights;
+  if (general)
+    return max_rows <= 16 ? launch_mode<HS, true, true>(p, n_requests, max_rows, stream)
+                          : launch_mode<HS, false, true>(p, n_requests, max_rows, stream);
+  return max_rows <= 16 ? launch_mode<HS, true, false>(p, n_requests, max_rows, stream)
+                        : launch_mode<HS, false, false>(p, n_requests, max_rows, stream);
 }
 
 }  // namespace
@@ -461,13 +525,16 @@ YALIS_API long long yalis_attention_mma_scratch_floats(int n_tokens, int nh, int
   return n_splits > 1 ? (long long)n_tokens * nh * n_splits * (hs + 2) : 0;
 }
 
-YALIS_API int yalis_paged_attention_mma(const void* q, int q_stride, void* out, int out_stride, const void* k_pool,
-                                        const void* v_pool, const int32_t* positions, const int32_t* q_start,
-                                        const int32_t* req_of_token, const int32_t* block_table, int table_width,
-                                        int page_size, int num_pages, int n_tokens, int n_requests, int max_q_len,
-                                        int nh, int g, int hs, float scale, int window, int n_splits, float* scratch,
-                                        int32_t* tickets, cudaStream_t stream) {
+// softcap 0: none.  With a cap, a sink, a factor other than 1 or exact_weights the general form of the kernel runs.
+YALIS_API int yalis_paged_attention_mma_general(const void* q, int q_stride, void* out, int out_stride, const void* k_pool,
+                                                const void* v_pool, const int32_t* positions, const int32_t* q_start,
+                                                const int32_t* req_of_token, const int32_t* block_table, int table_width,
+                                                int page_size, int num_pages, int n_tokens, int n_requests, int max_q_len,
+                                                int nh, int g, int hs, float scale, int window, int n_splits, float* scratch,
+                                                int32_t* tickets, float softcap, int sink, float out_scale,
+                                                int exact_weights, cudaStream_t stream) {
   if (n_tokens <= 0 || n_requests <= 0) return YALIS_OK;
+  if (softcap < 0.f) return YALIS_ERR_SHAPE;
   if (g <= 0 || nh % g != 0 || n_splits < 1 || max_q_len < 1) return YALIS_ERR_SHAPE;
   if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15) return YALIS_ERR_ALIGN;
   if ((q_stride % 8) || (out_stride % 2)) return YALIS_ERR_ALIGN;
@@ -482,6 +549,9 @@ YALIS_API int yalis_paged_attention_mma(const void* q, int q_stride, void* out, 
     if ((1 << sh) == page_size) p.page_shift = sh;
   p.nh = nh; p.g = g; p.per = nh / g;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.cap_log2 = softcap * 1.4426950408889634f;
+  p.scale_over_cap = softcap > 0.f ? scale / softcap : 0.f;
+  p.sink = sink; p.out_scale = out_scale; p.exact_weights = exact_weights;
   p.window = window; p.n_splits = n_splits;
   p.part_o = nullptr; p.part_ml = nullptr; p.tickets = tickets;
   if (n_splits > 1) {
@@ -542,6 +612,17 @@ int noalloc_scratch(unsigned char** ptr) {
 }
 
 }  // namespace
+
+YALIS_API int yalis_paged_attention_mma(const void* q, int q_stride, void* out, int out_stride, const void* k_pool,
+                                        const void* v_pool, const int32_t* positions, const int32_t* q_start,
+                                        const int32_t* req_of_token, const int32_t* block_table, int table_width,
+                                        int page_size, int num_pages, int n_tokens, int n_requests, int max_q_len,
+                                        int nh, int g, int hs, float scale, int window, int n_splits, float* scratch,
+                                        int32_t* tickets, cudaStream_t stream) {
+  return yalis_paged_attention_mma_general(q, q_stride, out, out_stride, k_pool, v_pool, positions, q_start, req_of_token,
+                                           block_table, table_width, page_size, num_pages, n_tokens, n_requests, max_q_len,
+                                           nh, g, hs, scale, window, n_splits, scratch, tickets, 0.f, 0, 1.0f, 0, stream);
+}
 
 YALIS_API long long yalis_paged_attention_mma_noalloc_needed(int n_tokens, int n_requests, int nh, int g, int hs,
                                                              int n_splits, long long* ticket_bytes,

@@ -22,17 +22,25 @@ namespace {
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
 
-// ---- short causal convolution over time, per channel, then silu -----------------------------------
-//   y_t[c] = sum_j w[c][K-1-j] x_(t-j)[c],  x before the request's start = 0
+// ---- what the delta rule reads: convolution, unit length, decay and write strength ------------------
+//   y_t[c] = silu(sum_j w[c][K-1-j] x_(t-j)[c]),  x before the request's start = 0
 // The last K-1 inputs of every request are kept in its slot: tail[c][0..K-2], oldest first.
+// With kv_heads > 0 the first 2 * kv_heads * dim channels are the heads of q and then of k: each head is
+// brought to unit length, x / sqrt(sum x^2 + eps), and q multiplied by q_scale.  With a_raw the decay
+// g = exp(-exp(a_log[h]) * softplus(a_raw + dt_bias)) (per head, or per head and key channel) and the write
+// strength beta = sigmoid(b_raw) are computed beside it, in float32.
 constexpr int kMaxTaps = 16;
 
 template <typename T>
-__global__ void short_conv_silu_kernel(const T* __restrict__ x, int x_stride, const float* __restrict__ w,
-                                       const float* __restrict__ tail, size_t slot_stride,
-                                       const int32_t* __restrict__ req_of_token, const int32_t* __restrict__ q_start,
-                                       const int32_t* __restrict__ slots, float* __restrict__ out, int out_stride,
-                                       int channels, int taps) {
+__global__ void delta_prepare_kernel(const T* __restrict__ x, int x_stride, const float* __restrict__ w,
+                                     const float* __restrict__ tail, size_t slot_stride,
+                                     const int32_t* __restrict__ req_of_token, const int32_t* __restrict__ q_start,
+                                     const int32_t* __restrict__ slots, float* __restrict__ out, int out_stride,
+                                     int channels, int taps, int kv_heads, int dim, float q_scale, float unit_eps,
+                                     const T* __restrict__ a_raw, int a_stride, int a_cols,
+                                     const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                                     const T* __restrict__ b_raw, int b_stride, int heads, float* __restrict__ g_out,
+                                     float* __restrict__ beta_out) {
   pdl_launch_dependents();
   pdl_wait();
   const int n = blockIdx.x;
@@ -40,7 +48,8 @@ __global__ void short_conv_silu_kernel(const T* __restrict__ x, int x_stride, co
   if (req < 0) return;
   const int i = n - q_start[req];                 // index of the token in its request's portion
   const float* tl = tail + (size_t)slots[req] * slot_stride;
-  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
+  float* row = out + (size_t)n * out_stride;
+  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
     float acc = 0.f;
     for (int j = taps - 1; j >= 0; --j) {         // oldest input first: a fixed order of additions
       float xv;
@@ -48,7 +57,28 @@ __global__ void short_conv_silu_kernel(const T* __restrict__ x, int x_stride, co
       else xv = tl[(size_t)c * (taps - 1) + (taps - 1 + i - j)];
       acc = __fmaf_rn(w[(size_t)c * taps + (taps - 1 - j)], xv, acc);
     }
-    out[(size_t)n * out_stride + c] = silu_exact(acc);
+    row[c] = silu_exact(acc);
+  }
+  if (a_raw != nullptr) {
+    const int per = a_cols / heads;               // 1, or dim
+    for (int c = threadIdx.x; c < a_cols; c += blockDim.x) {
+      const float a = to_f32<T>(a_raw[(size_t)n * a_stride + c]) + dt_bias[c];
+      g_out[(size_t)n * a_cols + c] = expf(-expf(a_log[c / per]) * softplus_f(a));
+    }
+    for (int h = threadIdx.x; h < heads; h += blockDim.x)
+      beta_out[(size_t)n * heads + h] = sigmoid_f(to_f32<T>(b_raw[(size_t)n * b_stride + h]));
+  }
+  if (kv_heads > 0) {
+    __syncthreads();                              // the block reads back what it wrote itself
+    const int lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int hh = threadIdx.x >> 5; hh < 2 * kv_heads; hh += nw) {     // q heads, then k heads
+      float* v = row + (size_t)hh * dim;
+      float ss = 0.f;
+      for (int d = lane; d < dim; d += 32) ss = __fmaf_rn(v[d], v[d], ss);
+      ss = warp_sum(ss);
+      const float r = (hh < kv_heads ? q_scale : 1.0f) / sqrtf(ss + unit_eps);
+      for (int d = lane; d < dim; d += 32) v[d] *= r;
+    }
   }
 }
 
@@ -82,25 +112,35 @@ __global__ void short_conv_tail_kernel(const T* __restrict__ x, int x_stride, fl
 // ---- the recurrence ------------------------------------------------------------------------------
 constexpr int kScanThreads = 128;
 constexpr int kRows = 16;            // rows of a column a thread keeps
+constexpr int kMaxTile = 16;         // tokens staged in shared memory at a time
 
 struct ScanParams {
   const float* q; int q_stride;      // [N, kv_heads * dim]
   const float* k; int k_stride;
   const float* v; int v_stride;      // [N, heads * vdim]
-  const float* decay_const;          // DECAY 0: [heads]
-  const void* a_raw; int a_stride;   // DECAY 1: [N, heads]; DECAY 2: [N, heads * dim]  (model dtype)
-  const float* a_log;                // [heads]
-  const float* dt_bias;              // [heads] or [heads * dim]
-  const void* b_raw; int b_stride;   // DELTA: [N, heads]  (model dtype)
+  const float* decay;                // DECAY 0: [heads]; 1: [N, heads]; 2: [N, heads * dim]
+  const float* beta;                 // DELTA: [N, heads]
   float* state; size_t slot_stride;  // per slot: [heads][vdim][dim_padded]
   float* out; int out_stride;        // [N, heads * vdim]
   const int32_t* q_start; const int32_t* slots;
   int heads, kv_heads, dim, dim_padded, vdim, lanes, tile;
-  int normalize; float q_scale, unit_eps;
+  int wide;                          // 1: rows of q, k and the decay may be copied 16 bytes at a time
 };
 
+__device__ __forceinline__ void copy_async4(float* smem, const float* gmem) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void copy_async16(float* smem, const float* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
 // DECAY: 0 constant per head, 1 scalar per token and head, 2 vector per token, head and key channel.
-template <typename T, bool DELTA, int DECAY>
+// The tokens of a request are staged through two buffers in shared memory: while one tile is walked, the
+// asynchronous copies of the next are in flight.
+template <bool DELTA, int DECAY>
 __global__ void __launch_bounds__(kScanThreads) state_scan_kernel(const ScanParams p) {
   extern __shared__ __align__(16) float sm[];
   pdl_launch_dependents();
@@ -114,12 +154,56 @@ __global__ void __launch_bounds__(kScanThreads) state_scan_kernel(const ScanPara
   const bool live = j < p.vdim;
   const int kvh = h / (p.heads / p.kv_heads);
   const int D = p.dim, Dp = p.dim_padded, V = p.vdim, TT = p.tile;
-  float* qs = sm;                                  // [TT][width]
-  float* ks = qs + (size_t)TT * width;
-  float* gv = ks + (size_t)TT * width;             // DECAY 2 only
-  float* vs = gv + (DECAY == 2 ? (size_t)TT * width : 0);   // [TT][cols]
-  float* bs = vs + (size_t)TT * cols;              // beta [TT]
-  float* gs = bs + TT;                             // scalar decay [TT]
+  // one buffer: q [TT][width], k [TT][width], decay vectors [TT][width] (DECAY 2), v [TT][cols], beta [TT], decay [TT]
+  const size_t buf_floats = ((size_t)(DECAY == 2 ? 3 : 2) * TT * width + (size_t)TT * cols + 2 * TT + 3) & ~(size_t)3;
+  const int vec_cols = DECAY == 2 ? 3 : 2;
+
+  // what no copy ever writes: the rows past dim (zeros; ones for the decay)
+  for (int e = tid; e < 2 * vec_cols * TT * width; e += kScanThreads) {
+    const int b = e / (vec_cols * TT * width), r = e - b * (vec_cols * TT * width);
+    const int which = r / (TT * width), d = r % width;
+    if (d >= D) sm[(size_t)b * buf_floats + r] = which == 2 ? 1.f : 0.f;
+  }
+
+  auto issue = [&](int t0, int b) {
+    float* qs = sm + (size_t)b * buf_floats;
+    float* ks = qs + (size_t)TT * width;
+    float* gv = ks + (size_t)TT * width;
+    float* vs = qs + (size_t)vec_cols * TT * width;
+    float* bs = vs + (size_t)TT * cols;
+    float* gs = bs + TT;
+    const int tt = min(TT, q_len - t0);
+    if (p.wide) {
+      const int quads = D >> 2;
+      for (int e = tid; e < tt * quads; e += kScanThreads) {
+        const int t = e / quads, d = (e - t * quads) << 2;
+        const size_t n = (size_t)(t_begin + t0 + t);
+        copy_async16(qs + t * width + d, p.q + n * p.q_stride + (size_t)kvh * D + d);
+        copy_async16(ks + t * width + d, p.k + n * p.k_stride + (size_t)kvh * D + d);
+        if (DECAY == 2) copy_async16(gv + t * width + d, p.decay + (n * p.heads + h) * D + d);
+      }
+    } else {
+      for (int e = tid; e < tt * D; e += kScanThreads) {
+        const int t = e / D, d = e - t * D;
+        const size_t n = (size_t)(t_begin + t0 + t);
+        copy_async4(qs + t * width + d, p.q + n * p.q_stride + (size_t)kvh * D + d);
+        copy_async4(ks + t * width + d, p.k + n * p.k_stride + (size_t)kvh * D + d);
+        if (DECAY == 2) copy_async4(gv + t * width + d, p.decay + (n * p.heads + h) * D + d);
+      }
+    }
+    for (int e = tid; e < tt * cols; e += kScanThreads) {
+      const int t = e / cols, cc = e - t * cols;
+      const int jj = blockIdx.x * cols + cc;
+      if (jj < V) copy_async4(vs + e, p.v + (size_t)(t_begin + t0 + t) * p.v_stride + (size_t)h * V + jj);
+      else vs[e] = 0.f;
+    }
+    if (tid < tt) {
+      const size_t n = (size_t)(t_begin + t0 + tid);
+      if (DELTA) copy_async4(bs + tid, p.beta + n * p.heads + h);
+      if (DECAY == 1) copy_async4(gs + tid, p.decay + n * p.heads + h);
+    }
+    copy_async_commit();
+  };
 
   float* sp = p.state + (size_t)p.slots[req] * p.slot_stride + ((size_t)h * V + (live ? j : 0)) * Dp;
   float S[kRows];
@@ -130,68 +214,34 @@ __global__ void __launch_bounds__(kScanThreads) state_scan_kernel(const ScanPara
     if (live && d < Dp) x = *reinterpret_cast<const float4*>(sp + d);
     S[4 * i] = x.x; S[4 * i + 1] = x.y; S[4 * i + 2] = x.z; S[4 * i + 3] = x.w;
   }
-  const float exp_a = DECAY != 0 ? expf(p.a_log[h]) : 0.f;
-  const float g_const = DECAY == 0 ? p.decay_const[h] : 1.f;
-  const T* a_raw = reinterpret_cast<const T*>(p.a_raw);
-  const T* b_raw = reinterpret_cast<const T*>(p.b_raw);
+  const float g_const = DECAY == 0 ? p.decay[h] : 1.f;
 
-  for (int t0 = 0; t0 < q_len; t0 += TT) {
+  issue(0, 0);
+  int b = 0;
+  for (int t0 = 0; t0 < q_len; t0 += TT, b ^= 1) {
     const int tt = min(TT, q_len - t0);
-    __syncthreads();
-    for (int e = tid; e < tt * width; e += kScanThreads) {
-      const int t = e / width, d = e - t * width;
-      const size_t n = (size_t)(t_begin + t0 + t);
-      const bool in = d < D;
-      qs[e] = in ? p.q[n * p.q_stride + (size_t)kvh * D + d] : 0.f;
-      ks[e] = in ? p.k[n * p.k_stride + (size_t)kvh * D + d] : 0.f;
-      if (DECAY == 2) {
-        float g = 1.f;
-        if (in) {
-          const float a = to_f32<T>(a_raw[n * p.a_stride + (size_t)h * D + d]) + p.dt_bias[(size_t)h * D + d];
-          g = expf(-exp_a * softplus_f(a));
-        }
-        gv[e] = g;
-      }
-    }
-    for (int e = tid; e < tt * cols; e += kScanThreads) {
-      const int t = e / cols, cc = e - t * cols;
-      const int jj = blockIdx.x * cols + cc;
-      vs[e] = jj < V ? p.v[(size_t)(t_begin + t0 + t) * p.v_stride + (size_t)h * V + jj] : 0.f;
-    }
-    if (tid < tt) {
-      const size_t n = (size_t)(t_begin + t0 + tid);
-      if (DELTA) bs[tid] = sigmoid_f(to_f32<T>(b_raw[n * p.b_stride + h]));
-      if (DECAY == 1) gs[tid] = expf(-exp_a * softplus_f(to_f32<T>(a_raw[n * p.a_stride + h]) + p.dt_bias[h]));
+    if (t0 + TT < q_len) {
+      issue(t0 + TT, b ^ 1);
+      copy_async_wait<1>();
+    } else {
+      copy_async_wait<0>();
     }
     __syncthreads();
-    if (p.normalize) {
-      // q and k of every token to unit length (q then scaled); a warp per token, sums in a fixed order
-      for (int t = tid >> 5; t < tt; t += kScanThreads / 32) {
-        float sq = 0.f, sk = 0.f;
-        for (int d = tid & 31; d < D; d += 32) {
-          const float a = qs[t * width + d], b = ks[t * width + d];
-          sq = __fmaf_rn(a, a, sq);
-          sk = __fmaf_rn(b, b, sk);
-        }
-        sq = warp_sum(sq);
-        sk = warp_sum(sk);
-        const float rq = p.q_scale / sqrtf(sq + p.unit_eps), rk = 1.0f / sqrtf(sk + p.unit_eps);
-        for (int d = tid & 31; d < D; d += 32) {
-          qs[t * width + d] *= rq;
-          ks[t * width + d] *= rk;
-        }
-      }
-      __syncthreads();
-    }
+    const float* qs = sm + (size_t)b * buf_floats;
+    const float* ks = qs + (size_t)TT * width;
+    const float* gv = ks + (size_t)TT * width;
+    const float* vs = qs + (size_t)vec_cols * TT * width;
+    const float* bs = vs + (size_t)TT * cols;
+    const float* gs = bs + TT;
     for (int t = 0; t < tt; ++t) {
       float kr[kRows], qr[kRows];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int d = (i * L + l) * 4;
         const float4 a = *reinterpret_cast<const float4*>(ks + (size_t)t * width + d);
-        const float4 b = *reinterpret_cast<const float4*>(qs + (size_t)t * width + d);
+        const float4 bq = *reinterpret_cast<const float4*>(qs + (size_t)t * width + d);
         kr[4 * i] = a.x; kr[4 * i + 1] = a.y; kr[4 * i + 2] = a.z; kr[4 * i + 3] = a.w;
-        qr[4 * i] = b.x; qr[4 * i + 1] = b.y; qr[4 * i + 2] = b.z; qr[4 * i + 3] = b.w;
+        qr[4 * i] = bq.x; qr[4 * i + 1] = bq.y; qr[4 * i + 2] = bq.z; qr[4 * i + 3] = bq.w;
       }
       if (DECAY == 2) {
 #pragma unroll
@@ -206,21 +256,34 @@ __global__ void __launch_bounds__(kScanThreads) state_scan_kernel(const ScanPara
       }
       float u = vs[t * cols + c];
       if (DELTA) {
-        float dot = 0.f;
+        // four chains of four, then a fixed tree: the order of additions is the same for every token
+        float d4[4];
 #pragma unroll
-        for (int r = 0; r < kRows; ++r) dot = __fmaf_rn(S[r], kr[r], dot);
+        for (int i = 0; i < 4; ++i) {
+          d4[i] = S[4 * i] * kr[4 * i];
+#pragma unroll
+          for (int e = 1; e < 4; ++e) d4[i] = __fmaf_rn(S[4 * i + e], kr[4 * i + e], d4[i]);
+        }
+        float dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
         for (int o = 1; o < L; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
         u = bs[t] * (u - dot);
       }
-      float o_acc = 0.f;
+      float o4[4];
 #pragma unroll
-      for (int r = 0; r < kRows; ++r) {
-        S[r] = __fmaf_rn(kr[r], u, S[r]);
-        o_acc = __fmaf_rn(S[r], qr[r], o_acc);
+      for (int i = 0; i < 4; ++i) {
+        S[4 * i] = __fmaf_rn(kr[4 * i], u, S[4 * i]);
+        o4[i] = S[4 * i] * qr[4 * i];
+#pragma unroll
+        for (int e = 1; e < 4; ++e) {
+          S[4 * i + e] = __fmaf_rn(kr[4 * i + e], u, S[4 * i + e]);
+          o4[i] = __fmaf_rn(S[4 * i + e], qr[4 * i + e], o4[i]);
+        }
       }
+      float o_acc = (o4[0] + o4[1]) + (o4[2] + o4[3]);
       for (int o = 1; o < L; o <<= 1) o_acc += __shfl_xor_sync(0xffffffffu, o_acc, o);
       if (live && l == 0) p.out[(size_t)(t_begin + t0 + t) * p.out_stride + (size_t)h * V + j] = o_acc;
     }
+    __syncthreads();                // the next round's copies overwrite the other buffer, which the round after reads
   }
   if (live) {
 #pragma unroll
@@ -262,17 +325,24 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, int o_stride,
 
 }  // namespace
 
-YALIS_API int yalis_short_conv_silu(const void* x, int dtype, int x_stride, const float* w, float* tail,
-                                    int64_t slot_stride, const int32_t* req_of_token, const int32_t* q_start,
-                                    const int32_t* slots, float* out, int out_stride, int n_tokens, int n_requests,
-                                    int channels, int taps, cudaStream_t stream) {
+// a_raw null: no decay and write strength are computed.  kv_heads 0: no head is brought to unit length.
+YALIS_API int yalis_delta_prepare(const void* x, int dtype, int x_stride, const float* w, float* tail,
+                                  int64_t slot_stride, const int32_t* req_of_token, const int32_t* q_start,
+                                  const int32_t* slots, float* out, int out_stride, int n_tokens, int n_requests,
+                                  int channels, int taps, int kv_heads, int dim, float q_scale, float unit_eps,
+                                  const void* a_raw, int a_stride, int a_cols, const float* a_log, const float* dt_bias,
+                                  const void* b_raw, int b_stride, int heads, float* g_out, float* beta_out,
+                                  cudaStream_t stream) {
   if (n_tokens <= 0) return YALIS_OK;
-  if (taps < 1 || taps > kMaxTaps || channels <= 0) return YALIS_ERR_SHAPE;
+  if (taps < 1 || taps > kMaxTaps || channels <= 0 || kv_heads < 0 || 2 * kv_heads * dim > channels) return YALIS_ERR_SHAPE;
+  if (a_raw && (heads <= 0 || a_cols % heads || !a_log || !dt_bias || !b_raw || !g_out || !beta_out)) return YALIS_ERR_SHAPE;
   const int by = (channels + 127) / 128;
+  const int threads = channels >= 1024 ? 256 : 128;
   YALIS_DISPATCH_DTYPE(dtype, T, {
-    int st = yalis_launch(short_conv_silu_kernel<T>, dim3(n_tokens, by), dim3(128), 0, stream, (const T*)x, x_stride, w,
-                          (const float*)tail, (size_t)slot_stride, req_of_token, q_start, slots, out, out_stride,
-                          channels, taps);
+    int st = yalis_launch(delta_prepare_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream, (const T*)x, x_stride, w,
+                          (const float*)tail, (size_t)slot_stride, req_of_token, q_start, slots, out, out_stride, channels,
+                          taps, kv_heads, dim, q_scale, unit_eps, (const T*)a_raw, a_stride, a_cols, a_log, dt_bias,
+                          (const T*)b_raw, b_stride, heads, g_out, beta_out);
     if (st != YALIS_OK || taps == 1) return st;
     return yalis_launch(short_conv_tail_kernel<T>, dim3(n_requests, by), dim3(128), 0, stream, (const T*)x, x_stride,
                         tail, (size_t)slot_stride, q_start, slots, channels, taps);
@@ -287,48 +357,50 @@ YALIS_API int yalis_state_scan_lanes(int dim) {
   return lanes;
 }
 
+template <bool DELTA, int DECAY>
+static int launch_scan(const ScanParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
+  static size_t allowed = 48 * 1024;
+  if (smem > allowed) {
+    if (cudaFuncSetAttribute(state_scan_kernel<DELTA, DECAY>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
+        cudaSuccess)
+      return YALIS_ERR_LAUNCH;
+    allowed = 200 * 1024;
+  }
+  return yalis_launch(state_scan_kernel<DELTA, DECAY>, grid, dim3(kScanThreads), smem, stream, p);
+}
+
+// decay_kind 0: decay [heads]; 1: decay [N, heads]; 2: decay [N, heads * dim].  beta [N, heads] with delta.
 YALIS_API int yalis_state_scan(const float* q, int q_stride, const float* k, int k_stride, const float* v, int v_stride,
-                               const float* decay_const, const void* a_raw, int a_stride, const float* a_log,
-                               const float* dt_bias, const void* b_raw, int b_stride, int raw_dtype, float* state,
-                               int64_t slot_stride, float* out, int out_stride, const int32_t* q_start,
-                               const int32_t* slots, int n_requests, int heads, int kv_heads, int dim, int vdim,
-                               int delta, int decay_kind, int normalize, float q_scale, float unit_eps,
-                               cudaStream_t stream) {
+                               const float* decay, int decay_kind, const float* beta, float* state, int64_t slot_stride,
+                               float* out, int out_stride, const int32_t* q_start, const int32_t* slots, int n_requests,
+                               int heads, int kv_heads, int dim, int vdim, int delta, cudaStream_t stream) {
   if (n_requests <= 0) return YALIS_OK;
   if (dim <= 0 || vdim <= 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || heads > 65535 || n_requests > 65535)
     return YALIS_ERR_SHAPE;
   const int lanes = yalis_state_scan_lanes(dim);
   if (lanes > 32) return YALIS_ERR_SHAPE;           // dim <= 512
-  if (decay_kind < 0 || decay_kind > 2 || (decay_kind == 0 && !decay_const) || (decay_kind != 0 && (!a_raw || !a_log || !dt_bias)) ||
-      (delta && !b_raw))
-    return YALIS_ERR_SHAPE;
+  if (decay_kind < 0 || decay_kind > 2 || !decay || (delta && !beta)) return YALIS_ERR_SHAPE;
   const int dim_padded = (dim + 3) & ~3;
   if ((slot_stride & 3) || ((uintptr_t)state & 15)) return YALIS_ERR_ALIGN;
   const int cols = kScanThreads / lanes, width = kRows * lanes;
   const size_t per_token = ((decay_kind == 2 ? 3 : 2) * (size_t)width + cols + 2) * sizeof(float);
-  int tile = (int)((40 * 1024) / per_token);
-  tile = tile > 16 ? 16 : (tile < 1 ? 1 : tile);
+  int tile = (int)((180 * 1024) / (2 * per_token));
+  tile = tile > kMaxTile ? kMaxTile : (tile < 1 ? 1 : tile);
   ScanParams p;
   p.q = q; p.q_stride = q_stride; p.k = k; p.k_stride = k_stride; p.v = v; p.v_stride = v_stride;
-  p.decay_const = decay_const; p.a_raw = a_raw; p.a_stride = a_stride; p.a_log = a_log; p.dt_bias = dt_bias;
-  p.b_raw = b_raw; p.b_stride = b_stride; p.state = state; p.slot_stride = (size_t)slot_stride; p.out = out;
+  p.decay = decay; p.beta = beta; p.state = state; p.slot_stride = (size_t)slot_stride; p.out = out;
   p.out_stride = out_stride; p.q_start = q_start; p.slots = slots; p.heads = heads; p.kv_heads = kv_heads;
-  p.dim = dim; p.dim_padded = dim_padded; p.vdim = vdim; p.lanes = lanes; p.tile = tile; p.normalize = normalize;
-  p.q_scale = q_scale; p.unit_eps = unit_eps;
+  p.dim = dim; p.dim_padded = dim_padded; p.vdim = vdim; p.lanes = lanes; p.tile = tile;
+  p.wide = (dim % 4 == 0 && q_stride % 4 == 0 && k_stride % 4 == 0 && !((uintptr_t)q & 15) && !((uintptr_t)k & 15) &&
+            (decay_kind != 2 || !((uintptr_t)decay & 15))) ? 1 : 0;
   const dim3 grid((vdim + cols - 1) / cols, heads, n_requests);
-  const size_t smem = per_token * tile;
-#define YALIS_SCAN(DELTA, DECAY) \
-  return yalis_launch(state_scan_kernel<T, DELTA, DECAY>, grid, dim3(kScanThreads), smem, stream, p)
-  YALIS_DISPATCH_DTYPE(raw_dtype, T, {
-    if (delta && decay_kind == 1) YALIS_SCAN(true, 1);
-    if (delta && decay_kind == 2) YALIS_SCAN(true, 2);
-    if (delta && decay_kind == 0) YALIS_SCAN(true, 0);
-    if (decay_kind == 0) YALIS_SCAN(false, 0);
-    if (decay_kind == 1) YALIS_SCAN(false, 1);
-    YALIS_SCAN(false, 2);
-  });
-#undef YALIS_SCAN
-  return YALIS_OK;
+  const size_t smem = 2 * ((per_token * tile + 15) & ~(size_t)15);
+  if (delta && decay_kind == 1) return launch_scan<true, 1>(p, grid, smem, stream);
+  if (delta && decay_kind == 2) return launch_scan<true, 2>(p, grid, smem, stream);
+  if (delta) return launch_scan<true, 0>(p, grid, smem, stream);
+  if (decay_kind == 0) return launch_scan<false, 0>(p, grid, smem, stream);
+  if (decay_kind == 1) return launch_scan<false, 1>(p, grid, smem, stream);
+  return launch_scan<false, 2>(p, grid, smem, stream);
 }
 
 YALIS_API int yalis_head_norm_gate(const float* o, int o_stride, const float* weight, const void* gate, int gate_stride,

@@ -165,11 +165,15 @@ def paged_attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Ten
                         q_start: torch.Tensor, req_of_token: torch.Tensor, block_table: torch.Tensor, max_q_len: int,
                         num_heads: int, num_kv_heads: int, head_dim: int, scale: Optional[float] = None,
                         window: Optional[int] = None, n_splits: int = 1,
-                        out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                        out: Optional[torch.Tensor] = None, softcap: Optional[float] = None, sink: bool = False,
+                        out_scale: float = 1.0, exact_weights: bool = False) -> torch.Tensor:
     """Tensor-core attention (bfloat16) of the step's tokens over the cache; the same
     semantics as ``paged_attention_generic``.  ``q_start`` int32 [R+1] gives each request's
     token range; ``max_q_len`` bounds the launch grid.  ``n_splits`` > 1 divides the keys of
     a request among blocks (decode steps) and needs scratch memory for the partial results.
+    ``softcap``, ``sink`` and ``out_scale`` as in ``paged_attention_generic``; with any of them, or with
+    ``exact_weights``, the softmax weights meet the values with 16 bits of mantissa (in two bfloat16 halves)
+    instead of 8.  ``out`` may be a column block of a wider matrix if it starts on a 16-byte boundary.
     """
     name = "paged_attention_mma"
     LAUNCHED["mma"] += 1
@@ -181,7 +185,9 @@ def paged_attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Ten
     need(block_table.shape[0] >= r, name, "block_table has fewer rows than requests")
     if out is None:
         out = torch.empty((n, num_heads * head_dim), dtype=q.dtype, device=q.device)
-    need(out.shape == (n, num_heads * head_dim) and out.dtype == q.dtype and out.is_contiguous(), name, "bad out tensor")
+    need(out.shape == (n, num_heads * head_dim) and out.dtype == q.dtype and out.stride(1) == 1
+         and out.stride(0) % 2 == 0 and out.data_ptr() % 16 == 0, name, "bad out tensor")
+    need(softcap is None or softcap > 0, name, "the soft cap must be positive")
     if scale is None:
         scale = 1.0 / math.sqrt(head_dim)
     scratch = tickets = None
@@ -192,11 +198,12 @@ def paged_attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Ten
         scratch = torch.empty(int(floats(i32(n), i32(num_heads), i32(head_dim), i32(n_splits))), dtype=torch.float32,
                               device=q.device)
         tickets = _tickets(q.device, r * num_kv_heads)
-    check(lib().yalis_paged_attention_mma(
+    check(lib().yalis_paged_attention_mma_general(
         ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(k_pool), ptr(v_pool), ptr(positions), ptr(q_start),
         ptr(req_of_token), ptr(block_table), i32(block_table.shape[1]), i32(k_pool.shape[2]), i32(k_pool.shape[0]),
         i32(n), i32(r), i32(max_q_len), i32(num_heads), i32(num_kv_heads), i32(head_dim), f32(scale), i32(window or 0),
-        i32(n_splits), ptr(scratch), ptr(tickets), stream()), name)
+        i32(n_splits), ptr(scratch), ptr(tickets), f32(softcap or 0.0), i32(int(sink)), f32(out_scale),
+        i32(int(exact_weights)), stream()), name)
     return out
 
 

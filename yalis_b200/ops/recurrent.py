@@ -55,15 +55,23 @@ def _index_arrays(name, n, req_of_token, q_start, slots):
          "slots must be int32 [R]")
 
 
-def short_conv_silu(x: torch.Tensor, weight: torch.Tensor, slot_rows: torch.Tensor, tail_offset: int,
-                    req_of_token: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
-    """silu of a causal convolution over time, per channel, continuing each request from the tail its slot keeps.
+def delta_prepare(x: torch.Tensor, weight: torch.Tensor, slot_rows: torch.Tensor, tail_offset: int,
+                  req_of_token: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, *, unit_heads: int = 0,
+                  dim: int = 0, q_scale: float = 1.0, unit_eps: float = 1e-6, a_raw: Optional[torch.Tensor] = None,
+                  a_log: Optional[torch.Tensor] = None, dt_bias: Optional[torch.Tensor] = None,
+                  b_raw: Optional[torch.Tensor] = None):
+    """What a delta rule reads, in one kernel: silu of a causal convolution over time, per channel, continuing each
+    request from the tail its slot keeps; the heads of q and k brought to unit length; decay and write strength.
 
-    ``x`` [N, C] (a column block of a wider matrix is fine), ``weight`` float32 [C, taps] with the current
-    token's tap last, ``slot_rows`` float32 [slots, row] with the tail [C, taps - 1] at ``tail_offset`` of each
-    row.  Returns float32 [N, C]; afterwards the tails hold the last ``taps - 1`` inputs of every request."""
-    name = "short_conv_silu"
-    need_cuda(name, x, weight, slot_rows, req_of_token, q_start, slots)
+    ``x`` [N, C] (a column block of a wider matrix is fine), ``weight`` float32 [C, taps] with the current token's
+    tap last, ``slot_rows`` float32 [slots, row] with the tail [C, taps - 1] at ``tail_offset`` of each row.  With
+    ``unit_heads`` = G > 0 the first 2 G ``dim`` channels are G heads of q and G of k: each becomes
+    x / sqrt(sum x^2 + unit_eps), q times ``q_scale``.  With ``a_raw`` ([N, heads] or [N, heads * dim]), ``a_log``
+    [heads], ``dt_bias`` (one per column of a_raw) and ``b_raw`` [N, heads]: g = exp(-exp(a_log) softplus(a_raw +
+    dt_bias)) and beta = sigmoid(b_raw).  Returns (float32 [N, C], g, beta), g and beta float32 or None; afterwards
+    the tails hold the last ``taps - 1`` inputs of every request."""
+    name = "delta_prepare"
+    need_cuda(name, x, weight, slot_rows, req_of_token, q_start, slots, a_raw, a_log, dt_bias, b_raw)
     need(x.dim() == 2 and x.stride(1) == 1, name, "x must be [N, C] with unit inner stride")
     n, c = x.shape
     need(weight.dtype == torch.float32 and weight.dim() == 2 and weight.shape[0] == c and weight.is_contiguous(), name,
@@ -72,31 +80,49 @@ def short_conv_silu(x: torch.Tensor, weight: torch.Tensor, slot_rows: torch.Tens
     need(1 <= taps <= 16, name, f"{taps} taps are not supported (1 to 16)")
     need(slot_rows.dtype == torch.float32 and slot_rows.dim() == 2 and slot_rows.is_contiguous()
          and tail_offset + c * (taps - 1) <= slot_rows.shape[1], name, "slot rows must be float32 [slots, row] that hold the tail")
+    need(unit_heads == 0 or (dim > 0 and 2 * unit_heads * dim <= c), name, "the heads of q and k must lie within the channels")
     _index_arrays(name, n, req_of_token, q_start, slots)
     out = torch.empty((n, c), dtype=torch.float32, device=x.device)
+    g = beta = None
+    heads = a_cols = 0
+    if a_raw is not None:
+        need(a_log is not None and dt_bias is not None and b_raw is not None, name, "a_raw comes with a_log, dt_bias and b_raw")
+        heads = a_log.numel()
+        need(a_raw.dim() == 2 and a_raw.shape[0] == n and a_raw.stride(1) == 1 and a_raw.dtype == x.dtype
+             and a_raw.shape[1] % heads == 0, name, "a_raw must be [N, heads] or [N, heads * dim] in the dtype of x")
+        a_cols = a_raw.shape[1]
+        need(a_log.dtype == torch.float32 and a_log.is_contiguous() and dt_bias.dtype == torch.float32
+             and dt_bias.shape == (a_cols,) and dt_bias.is_contiguous(), name, "a_log float32 [heads], dt_bias float32 per column of a_raw")
+        need(b_raw.shape == (n, heads) and b_raw.stride(1) == 1 and b_raw.dtype == x.dtype, name, "b_raw must be [N, heads] in the dtype of x")
+        g = torch.empty((n, a_cols), dtype=torch.float32, device=x.device)
+        beta = torch.empty((n, heads), dtype=torch.float32, device=x.device)
     tail = slot_rows.view(-1)[tail_offset:]
-    check(lib().yalis_short_conv_silu(ptr(x), i32(dtype_code(x.dtype)), i32(x.stride(0)), ptr(weight), ptr(tail),
-                                      i64(slot_rows.stride(0)), ptr(req_of_token), ptr(q_start), ptr(slots), ptr(out),
-                                      i32(c), i32(n), i32(slots.numel()), i32(c), i32(taps), stream()), name)
-    return out
+    check(lib().yalis_delta_prepare(
+        ptr(x), i32(dtype_code(x.dtype)), i32(x.stride(0)), ptr(weight), ptr(tail), i64(slot_rows.stride(0)),
+        ptr(req_of_token), ptr(q_start), ptr(slots), ptr(out), i32(c), i32(n), i32(slots.numel()), i32(c), i32(taps),
+        i32(unit_heads), i32(dim), f32(q_scale), f32(unit_eps), ptr(a_raw), i32(a_raw.stride(0) if a_raw is not None else 0),
+        i32(a_cols), ptr(a_log), ptr(dt_bias), ptr(b_raw), i32(b_raw.stride(0) if b_raw is not None else 0), i32(heads),
+        ptr(g), ptr(beta), stream()), name)
+    return out, g, beta
+
+
+def short_conv_silu(x: torch.Tensor, weight: torch.Tensor, slot_rows: torch.Tensor, tail_offset: int,
+                    req_of_token: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
+    """The convolution of ``delta_prepare`` alone: float32 [N, C]."""
+    return delta_prepare(x, weight, slot_rows, tail_offset, req_of_token, q_start, slots)[0]
 
 
 def state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, slot_rows: torch.Tensor, layout: StateLayout,
-               q_start: torch.Tensor, slots: torch.Tensor, *, kv_heads: int, delta: bool,
-               decay: Optional[torch.Tensor] = None, a_raw: Optional[torch.Tensor] = None,
-               a_log: Optional[torch.Tensor] = None, dt_bias: Optional[torch.Tensor] = None,
-               b_raw: Optional[torch.Tensor] = None, normalize: bool = False, q_scale: float = 1.0,
-               unit_eps: float = 1e-6) -> torch.Tensor:
+               q_start: torch.Tensor, slots: torch.Tensor, *, kv_heads: int, decay: torch.Tensor,
+               beta: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Walks every request's tokens in order through the recurrence, from and to the state in its slot.
 
-    Per head (S is [dim, vdim]):  S <- g S;  u = beta (v - S^T k) if ``delta`` else v;  S <- S + k u^T;  o = S^T q.
-    ``q``, ``k`` float32 [N, kv_heads * dim], ``v`` float32 [N, heads * vdim] (column blocks are fine).  The
-    decay g is ``decay`` (float32 [heads], constant), or exp(-exp(a_log) * softplus(a_raw + dt_bias)) with
-    ``a_raw`` [N, heads] (one per token and head) or [N, heads * dim] (per key channel too); beta is
-    sigmoid(``b_raw``) [N, heads].  ``normalize`` first brings q and k of every head to unit length
-    (x / sqrt(sum x^2 + unit_eps)) and multiplies q by ``q_scale``.  Returns float32 [N, heads * vdim]."""
+    Per head (S is [dim, vdim]):  S <- g S;  u = beta (v - S^T k) with ``beta`` (the delta rule), else u = v;
+    S <- S + k u^T;  o = S^T q.  ``q``, ``k`` float32 [N, kv_heads * dim], ``v`` float32 [N, heads * vdim] (column
+    blocks are fine).  ``decay`` float32: [heads] (constant), [N, heads] (per token) or [N, heads * dim] (per key
+    channel too); ``beta`` float32 [N, heads].  Returns float32 [N, heads * vdim]."""
     name = "state_scan"
-    need_cuda(name, q, k, v, slot_rows, q_start, slots, decay, a_raw, a_log, dt_bias, b_raw)
+    need_cuda(name, q, k, v, slot_rows, q_start, slots, decay, beta)
     h, d, vd = layout.heads, layout.dim, layout.vdim
     n = q.shape[0]
     for t, width, what in ((q, kv_heads * d, "q"), (k, kv_heads * d, "k"), (v, h * vd, "v")):
@@ -108,30 +134,20 @@ def state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, slot_rows: tor
          "slot rows must be float32 [slots, row], rows a multiple of four floats that hold the state")
     need(q_start.dtype == torch.int32 and slots.dtype == torch.int32 and slots.numel() == q_start.numel() - 1, name,
          "q_start int32 [R + 1], slots int32 [R]")
-    raw_code = dtype_code(torch.float32)
-    if decay is not None:
+    need(decay.dtype == torch.float32 and decay.is_contiguous(), name, "decay must be contiguous float32")
+    if decay.dim() == 1:
+        need(decay.shape == (h,), name, "a constant decay has one entry per head")
         kind = DECAY_CONSTANT
-        need(decay.dtype == torch.float32 and decay.shape == (h,) and decay.is_contiguous(), name, "decay must be float32 [heads]")
     else:
-        need(a_raw is not None and a_log is not None and dt_bias is not None, name, "a decay needs `decay` or a_raw, a_log and dt_bias")
-        need(a_raw.dim() == 2 and a_raw.shape[0] == n and a_raw.stride(1) == 1 and a_raw.shape[1] in (h, h * d), name,
-             "a_raw must be [N, heads] or [N, heads * dim]")
-        kind = DECAY_PER_TOKEN if a_raw.shape[1] == h and dt_bias.numel() == h else DECAY_PER_CHANNEL
-        need(a_raw.shape[1] == dt_bias.numel() and dt_bias.dtype == torch.float32 and dt_bias.is_contiguous(), name,
-             "dt_bias must be float32 with one entry per column of a_raw")
-        need(a_log.dtype == torch.float32 and a_log.shape == (h,) and a_log.is_contiguous(), name, "a_log must be float32 [heads]")
-        raw_code = dtype_code(a_raw.dtype)
-    if delta:
-        need(b_raw is not None and b_raw.shape == (n, h) and b_raw.stride(1) == 1, name, "b_raw must be [N, heads]")
-        need(a_raw is None or b_raw.dtype == a_raw.dtype, name, "a_raw and b_raw must have one dtype")
-        raw_code = dtype_code(b_raw.dtype)
+        need(decay.shape in ((n, h), (n, h * d)), name, "decay must be [heads], [N, heads] or [N, heads * dim]")
+        kind = DECAY_PER_TOKEN if decay.shape[1] == h else DECAY_PER_CHANNEL
+    if beta is not None:
+        need(beta.dtype == torch.float32 and beta.shape == (n, h) and beta.is_contiguous(), name, "beta must be float32 [N, heads]")
     out = torch.empty((n, h * vd), dtype=torch.float32, device=q.device)
     check(lib().yalis_state_scan(
-        ptr(q), i32(q.stride(0)), ptr(k), i32(k.stride(0)), ptr(v), i32(v.stride(0)), ptr(decay), ptr(a_raw),
-        i32(a_raw.stride(0) if a_raw is not None else 0), ptr(a_log), ptr(dt_bias), ptr(b_raw),
-        i32(b_raw.stride(0) if b_raw is not None else 0), i32(raw_code), ptr(slot_rows), i64(slot_rows.stride(0)),
-        ptr(out), i32(out.stride(0)), ptr(q_start), ptr(slots), i32(slots.numel()), i32(h), i32(kv_heads), i32(d),
-        i32(vd), i32(int(delta)), i32(kind), i32(int(normalize)), f32(q_scale), f32(unit_eps), stream()), name)
+        ptr(q), i32(q.stride(0)), ptr(k), i32(k.stride(0)), ptr(v), i32(v.stride(0)), ptr(decay), i32(kind), ptr(beta),
+        ptr(slot_rows), i64(slot_rows.stride(0)), ptr(out), i32(out.stride(0)), ptr(q_start), ptr(slots),
+        i32(slots.numel()), i32(h), i32(kv_heads), i32(d), i32(vd), i32(int(beta is not None)), stream()), name)
     return out
 
 

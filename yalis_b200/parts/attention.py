@@ -162,8 +162,21 @@ class GeneralAttention(Mixer, Projected):
     def cache_request(self) -> PagedKV:
         return PagedKV(self.g, self.hs, self.window, v_head_dim=None if self.vd == self.hs else self.vd)
 
+    def _tensor_core_form(self, dtype: torch.dtype) -> bool:
+        """bfloat16 steps whose keys and values have one head size the kernel is built for go to the tensor cores
+        (scores and the sum of weights in float32, the weights against V in two bfloat16 halves); float32 steps
+        and other shapes go to the exact kernel."""
+        return dtype == torch.bfloat16 and self.vd == self.hs and attn_ops.mma_supports(self.hs)
+
+    def _launch_shape(self, host):
+        """(longest portion, key splits): a step in which a request's rows fill at most one tile of 16 (single
+        tokens of up to 16 heads per group) may divide each request's keys among blocks."""
+        rows = host.max_q_len * (self.nh // self.g)
+        return host.max_q_len, (attn_ops.decode_splits(len(host.slots), self.g) if rows <= 16 else 1)
+
     def capture_key(self, host):
-        return None      # one kernel for every step: a block per token and head, its loop bounds read on the device
+        # the exact kernel launches the same for every step; the tensor-core one by the longest portion
+        return ("general_attention",) + self._launch_shape(host)
 
     def mixing_flops(self, q_len: int, ctx_before: int) -> float:
         keys = sum(min(ctx_before + t + 1, self.window or (ctx_before + t + 1)) for t in range(q_len)) if self.window \
@@ -178,6 +191,16 @@ class GeneralAttention(Mixer, Projected):
                         out_dtype=z.dtype, biases=self.biases, q_norm=self.q_norm, k_norm=self.k_norm,
                         norm_eps=self.norm_eps or 0.0, inv_freq=freq, k_pool=cache.k, v_pool=cache.v, block_table=table,
                         store=cache.writable, bad_flag=ctx.error_flag)
+        if self._tensor_core_form(z.dtype):
+            longest, splits = self._launch_shape(ctx.host)
+            direct = y.data_ptr() % 16 == 0 and y.stride(0) % 2 == 0
+            out = attn_ops.paged_attention_mma(q, cache.k, cache.v, ctx.positions, ctx.q_start, ctx.req_of_token, table, longest,
+                                               self.nh, self.g, self.hs, scale=self.scale, window=self.window, n_splits=splits,
+                                               out=y if direct else None, softcap=self.softcap, sink=self.sink,
+                                               out_scale=self.out_scale, exact_weights=True)
+            if not direct:
+                y.copy_(out)
+            return
         attn_ops.paged_attention_generic(q, cache.k, cache.v, ctx.positions, ctx.req_of_token, table, self.nh, self.g, self.hs,
                                          scale=self.scale, window=self.window, out=y, v_head_dim=self.vd,
                                          softcap=self.softcap, sink=self.sink, out_scale=self.out_scale)

@@ -97,8 +97,7 @@ class Retention(_ProjectedMixer):
         freq = self.position.rotary_frequencies(self.position.head_dim, z.device) if self.position is not None else None
         q, k, v = qkv_prepare(z, (0, hd, 2 * hd), self.h, self.h, self.d, self.vd, ctx.positions, ctx.req_of_token,
                               out_dtype=torch.float32, inv_freq=freq, k_scale=self.d ** -0.5)
-        o = rec_ops.state_scan(q, k, v, cache.state, self.layout, ctx.q_start, ctx.slots, kv_heads=self.h, delta=False,
-                               decay=self.decay)
+        o = rec_ops.state_scan(q, k, v, cache.state, self.layout, ctx.q_start, ctx.slots, kv_heads=self.h, decay=self.decay)
         rec_ops.head_norm_gate(o, self.h, self.vd, self.eps, ctx.req_of_token, y, gate=z[:, 2 * hd + hv:2 * hd + 2 * hv],
                                gate_kind=rec_ops.GATE_SILU, out_scale=self.out_scale)
 
@@ -178,12 +177,13 @@ class GatedDelta(_ProjectedMixer):
 
     def mix(self, z: torch.Tensor, ctx, cache: SlotStateCache, y: torch.Tensor) -> None:
         gd = self.g * self.d
-        conv = rec_ops.short_conv_silu(self._block(z, "qkv"), self.conv_w, cache.state, self.layout.state_floats,
-                                       ctx.req_of_token, ctx.q_start, ctx.slots)
         a_raw = linear(self._block(z, "a1"), self.w_a2) if self.decay_kind == "channel" else self._block(z, "a")
+        conv, decay, beta = rec_ops.delta_prepare(
+            self._block(z, "qkv"), self.conv_w, cache.state, self.layout.state_floats, ctx.req_of_token, ctx.q_start, ctx.slots,
+            unit_heads=self.g, dim=self.d, q_scale=self.d ** -0.5, unit_eps=self.UNIT_EPS, a_raw=a_raw, a_log=self.a_log,
+            dt_bias=self.dt_bias, b_raw=self._block(z, "b"))
         o = rec_ops.state_scan(conv[:, :gd], conv[:, gd:2 * gd], conv[:, 2 * gd:], cache.state, self.layout, ctx.q_start,
-                               ctx.slots, kv_heads=self.g, delta=True, a_raw=a_raw, a_log=self.a_log, dt_bias=self.dt_bias,
-                               b_raw=self._block(z, "b"), normalize=True, q_scale=self.d ** -0.5, unit_eps=self.UNIT_EPS)
+                               ctx.slots, kv_heads=self.g, decay=decay, beta=beta)
         if self.gate_kind == "silu":
             gate, kind = self._block(z, "g"), rec_ops.GATE_SILU
         else:
