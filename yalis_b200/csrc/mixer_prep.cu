@@ -31,10 +31,12 @@ struct PrepParams {
 // One warp per (token, head): heads [0, nq) are queries, [nq, nq + nk) keys, [nq + nk, nq + 2 nk) values.
 template <typename T, typename TO>
 __global__ void qkv_prepare_kernel(const PrepParams p) {
-  __shared__ float xs[kMaxHeadDim];
+  extern __shared__ float xs_all[];           // a row of `width_max` floats per warp
   pdl_launch_dependents();
   pdl_wait();
-  const int n = blockIdx.x, head = blockIdx.y, lane = threadIdx.x;
+  const int n = blockIdx.x, head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (head >= p.nq + 2 * p.nk) return;
+  float* xs = xs_all + (size_t)(threadIdx.x >> 5) * (p.dim > p.vdim ? p.dim : p.vdim);
   const int req = p.req_of_token[n];
   if (req < 0) return;
   const int pos = p.positions[n];
@@ -109,6 +111,31 @@ __global__ void activation_kernel(const T* __restrict__ x, int x_stride, T* __re
   }
 }
 
+// The same, eight elements a thread, for bfloat16 rows that start on 16-byte boundaries and whose width is a
+// multiple of 8.  grid: (ceil(cols / 8 / 256), rows).
+__device__ __forceinline__ float act_value(float z, int act) {
+  if (act == 0) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
+  if (act == 1) return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+  return silu_exact(z);
+}
+
+__global__ void activation_bf16x8_kernel(const __nv_bfloat16* __restrict__ x, int x_stride, __nv_bfloat16* __restrict__ y,
+                                         int y_stride, int cols, int act) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c >= cols) return;
+  const size_t r = blockIdx.y;
+  uint4 raw = *reinterpret_cast<const uint4*>(x + r * x_stride + c);
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 z = __bfloat1622float2(h[i]);
+    h[i] = __floats2bfloat162_rn(act_value(z.x, act), act_value(z.y, act));
+  }
+  *reinterpret_cast<uint4*>(y + r * y_stride + c) = raw;
+}
+
 // x[n, :] += other[n, :] + vec[:]   (either may be absent)
 __global__ void add_rows_vector_kernel(float* __restrict__ x, const float* __restrict__ other,
                                        const float* __restrict__ vec, int rows, int cols) {
@@ -147,13 +174,15 @@ YALIS_API int yalis_qkv_prepare(const void* src, int dtype, int src_stride, int 
   p.v_out = v_out; p.v_out_stride = v_out_stride; p.k_pool = k_pool; p.v_pool = v_pool; p.block_table = block_table;
   p.table_width = table_width; p.page_size = page_size; p.num_pages = num_pages; p.positions = positions;
   p.req_of_token = req_of_token; p.nq = nq; p.nk = nk; p.dim = dim; p.vdim = vdim; p.bad_page = bad_page;
-  const dim3 grid(n_tokens, nq + 2 * nk);
+  const int warps = 4;
+  const dim3 grid(n_tokens, (nq + 2 * nk + warps - 1) / warps);
+  const size_t smem = (size_t)warps * (dim > vdim ? dim : vdim) * sizeof(float);
   if (dtype == YALIS_F32 && out_dtype == YALIS_F32)
-    return yalis_launch(qkv_prepare_kernel<float, float>, grid, dim3(32), 0, stream, p);
+    return yalis_launch(qkv_prepare_kernel<float, float>, grid, dim3(32 * warps), smem, stream, p);
   if (dtype == YALIS_BF16 && out_dtype == YALIS_BF16)
-    return yalis_launch(qkv_prepare_kernel<__nv_bfloat16, __nv_bfloat16>, grid, dim3(32), 0, stream, p);
+    return yalis_launch(qkv_prepare_kernel<__nv_bfloat16, __nv_bfloat16>, grid, dim3(32 * warps), smem, stream, p);
   if (dtype == YALIS_BF16 && out_dtype == YALIS_F32)
-    return yalis_launch(qkv_prepare_kernel<__nv_bfloat16, float>, grid, dim3(32), 0, stream, p);
+    return yalis_launch(qkv_prepare_kernel<__nv_bfloat16, float>, grid, dim3(32 * warps), smem, stream, p);
   return YALIS_ERR_DTYPE;
 }
 
@@ -163,6 +192,10 @@ YALIS_API int yalis_activation(const void* x, int x_stride, void* y, int y_strid
   if (act < 0 || act > 2) return YALIS_ERR_SHAPE;
   const size_t total = (size_t)rows * cols;
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  if (dtype == YALIS_BF16 && cols % 8 == 0 && x_stride % 8 == 0 && y_stride % 8 == 0 && !((uintptr_t)x & 15) &&
+      !((uintptr_t)y & 15) && rows <= 65535)
+    return yalis_launch(activation_bf16x8_kernel, dim3((cols / 8 + 127) / 128, rows), dim3(128), 0, stream,
+                        (const __nv_bfloat16*)x, x_stride, (__nv_bfloat16*)y, y_stride, cols, act);
   YALIS_DISPATCH_DTYPE(dtype, T,
                        return yalis_launch(activation_kernel<T>, dim3(blocks), dim3(256), 0, stream, (const T*)x, x_stride,
                                            (T*)y, y_stride, rows, cols, act));

@@ -159,10 +159,11 @@ __global__ void __launch_bounds__(kScanThreads) state_scan_kernel(const ScanPara
   const int vec_cols = DECAY == 2 ? 3 : 2;
 
   // what no copy ever writes: the rows past dim (zeros; ones for the decay)
-  for (int e = tid; e < 2 * vec_cols * TT * width; e += kScanThreads) {
-    const int b = e / (vec_cols * TT * width), r = e - b * (vec_cols * TT * width);
-    const int which = r / (TT * width), d = r % width;
-    if (d >= D) sm[(size_t)b * buf_floats + r] = which == 2 ? 1.f : 0.f;
+  const int pad = width - D;
+  for (int e = tid; e < 2 * vec_cols * TT * pad; e += kScanThreads) {
+    const int row = e / pad, d = D + (e - row * pad);          // row: (buffer, array, token)
+    const int b = row / (vec_cols * TT), r = row - b * (vec_cols * TT);
+    sm[(size_t)b * buf_floats + (size_t)r * width + d] = (r / TT) == 2 ? 1.f : 0.f;
   }
 
   auto issue = [&](int t0, int b) {
@@ -300,19 +301,19 @@ __global__ void __launch_bounds__(kScanThreads) state_scan_kernel(const ScanPara
 template <typename T>
 __global__ void head_norm_gate_kernel(const float* __restrict__ o, int o_stride, const float* __restrict__ weight,
                                       const T* __restrict__ gate, int gate_stride, int gate_kind, T* __restrict__ y,
-                                      int y_stride, const int32_t* __restrict__ req_of_token, int vdim, float eps,
-                                      float out_scale) {
-  __shared__ float scratch[32];
+                                      int y_stride, const int32_t* __restrict__ req_of_token, int heads, int vdim,
+                                      float eps, float out_scale) {
   pdl_launch_dependents();
   pdl_wait();
-  const int n = blockIdx.x, h = blockIdx.y;
-  if (req_of_token[n] < 0) return;
+  // a warp per (token, head): the sum of squares in a fixed order whatever the block holds
+  const int n = blockIdx.x, h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (h >= heads || req_of_token[n] < 0) return;
   const float* op = o + (size_t)n * o_stride + (size_t)h * vdim;
   float ss = 0.f;
-  for (int d = threadIdx.x; d < vdim; d += blockDim.x) ss = __fmaf_rn(op[d], op[d], ss);
-  ss = block_sum(ss, scratch);
+  for (int d = lane; d < vdim; d += 32) ss = __fmaf_rn(op[d], op[d], ss);
+  ss = warp_sum(ss);
   const float r = 1.0f / sqrtf(ss / (float)vdim + eps);
-  for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
+  for (int d = lane; d < vdim; d += 32) {
     float val = op[d] * r;
     if (weight) val *= weight[d];
     if (gate_kind) {
@@ -370,10 +371,11 @@ static int launch_scan(const ScanParams& p, dim3 grid, size_t smem, cudaStream_t
 }
 
 // decay_kind 0: decay [heads]; 1: decay [N, heads]; 2: decay [N, heads * dim].  beta [N, heads] with delta.
+// max_q_len: the longest portion of the step if the caller knows it (0: not known); it only bounds the staging tile.
 YALIS_API int yalis_state_scan(const float* q, int q_stride, const float* k, int k_stride, const float* v, int v_stride,
                                const float* decay, int decay_kind, const float* beta, float* state, int64_t slot_stride,
                                float* out, int out_stride, const int32_t* q_start, const int32_t* slots, int n_requests,
-                               int heads, int kv_heads, int dim, int vdim, int delta, cudaStream_t stream) {
+                               int heads, int kv_heads, int dim, int vdim, int delta, int max_q_len, cudaStream_t stream) {
   if (n_requests <= 0) return YALIS_OK;
   if (dim <= 0 || vdim <= 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || heads > 65535 || n_requests > 65535)
     return YALIS_ERR_SHAPE;
@@ -386,6 +388,7 @@ YALIS_API int yalis_state_scan(const float* q, int q_stride, const float* k, int
   const size_t per_token = ((decay_kind == 2 ? 3 : 2) * (size_t)width + cols + 2) * sizeof(float);
   int tile = (int)((180 * 1024) / (2 * per_token));
   tile = tile > kMaxTile ? kMaxTile : (tile < 1 ? 1 : tile);
+  if (max_q_len > 0 && tile > max_q_len) tile = max_q_len;      // single tokens: small blocks, many of them per SM
   ScanParams p;
   p.q = q; p.q_stride = q_stride; p.k = k; p.k_stride = k_stride; p.v = v; p.v_stride = v_stride;
   p.decay = decay; p.beta = beta; p.state = state; p.slot_stride = (size_t)slot_stride; p.out = out;
@@ -408,10 +411,10 @@ YALIS_API int yalis_head_norm_gate(const float* o, int o_stride, const float* we
                                    int n_tokens, int heads, int vdim, float eps, float out_scale, cudaStream_t stream) {
   if (n_tokens <= 0) return YALIS_OK;
   if (heads <= 0 || heads > 65535 || vdim <= 0 || gate_kind < 0 || gate_kind > 2 || (gate_kind && !gate)) return YALIS_ERR_SHAPE;
-  const int threads = vdim <= 32 ? 32 : (vdim <= 64 ? 64 : 128);
+  const int warps = heads < 4 ? heads : 4;
   YALIS_DISPATCH_DTYPE(dtype, T,
-                       return yalis_launch(head_norm_gate_kernel<T>, dim3(n_tokens, heads), dim3(threads), 0, stream, o,
-                                           o_stride, weight, (const T*)gate, gate_stride, gate_kind, (T*)y, y_stride,
-                                           req_of_token, vdim, eps, out_scale));
+                       return yalis_launch(head_norm_gate_kernel<T>, dim3(n_tokens, (heads + warps - 1) / warps),
+                                           dim3(32 * warps), 0, stream, o, o_stride, weight, (const T*)gate, gate_stride,
+                                           gate_kind, (T*)y, y_stride, req_of_token, heads, vdim, eps, out_scale));
   return YALIS_OK;
 }

@@ -114,13 +114,14 @@ def short_conv_silu(x: torch.Tensor, weight: torch.Tensor, slot_rows: torch.Tens
 
 def state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, slot_rows: torch.Tensor, layout: StateLayout,
                q_start: torch.Tensor, slots: torch.Tensor, *, kv_heads: int, decay: torch.Tensor,
-               beta: Optional[torch.Tensor] = None) -> torch.Tensor:
+               beta: Optional[torch.Tensor] = None, max_q_len: int = 0) -> torch.Tensor:
     """Walks every request's tokens in order through the recurrence, from and to the state in its slot.
 
     Per head (S is [dim, vdim]):  S <- g S;  u = beta (v - S^T k) with ``beta`` (the delta rule), else u = v;
     S <- S + k u^T;  o = S^T q.  ``q``, ``k`` float32 [N, kv_heads * dim], ``v`` float32 [N, heads * vdim] (column
     blocks are fine).  ``decay`` float32: [heads] (constant), [N, heads] (per token) or [N, heads * dim] (per key
-    channel too); ``beta`` float32 [N, heads].  Returns float32 [N, heads * vdim]."""
+    channel too); ``beta`` float32 [N, heads].  ``max_q_len``: the longest portion of the step if known (it bounds
+    the tile of tokens staged in shared memory, nothing else).  Returns float32 [N, heads * vdim]."""
     name = "state_scan"
     need_cuda(name, q, k, v, slot_rows, q_start, slots, decay, beta)
     h, d, vd = layout.heads, layout.dim, layout.vdim
@@ -147,7 +148,7 @@ def state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, slot_rows: tor
     check(lib().yalis_state_scan(
         ptr(q), i32(q.stride(0)), ptr(k), i32(k.stride(0)), ptr(v), i32(v.stride(0)), ptr(decay), i32(kind), ptr(beta),
         ptr(slot_rows), i64(slot_rows.stride(0)), ptr(out), i32(out.stride(0)), ptr(q_start), ptr(slots),
-        i32(slots.numel()), i32(h), i32(kv_heads), i32(d), i32(vd), i32(int(beta is not None)), stream()), name)
+        i32(slots.numel()), i32(h), i32(kv_heads), i32(d), i32(vd), i32(int(beta is not None)), i32(max_q_len), stream()), name)
     return out
 
 

@@ -55,7 +55,9 @@ class _ProjectedMixer(Mixer, Projected):
         return self.project_and_mix(x, ctx, cache)
 
     def capture_key(self, host):
-        return None      # the kernels read the step's arrays on the device; their grids follow the shapes alone
+        # the kernels read the step's arrays on the device and their grids follow the shapes alone; only the tile of
+        # tokens that the recurrence stages at a time follows the longest portion, up to 16
+        return min(host.max_q_len, 16)
 
 
 class Retention(_ProjectedMixer):
@@ -97,7 +99,8 @@ class Retention(_ProjectedMixer):
         freq = self.position.rotary_frequencies(self.position.head_dim, z.device) if self.position is not None else None
         q, k, v = qkv_prepare(z, (0, hd, 2 * hd), self.h, self.h, self.d, self.vd, ctx.positions, ctx.req_of_token,
                               out_dtype=torch.float32, inv_freq=freq, k_scale=self.d ** -0.5)
-        o = rec_ops.state_scan(q, k, v, cache.state, self.layout, ctx.q_start, ctx.slots, kv_heads=self.h, decay=self.decay)
+        o = rec_ops.state_scan(q, k, v, cache.state, self.layout, ctx.q_start, ctx.slots, kv_heads=self.h, decay=self.decay,
+                               max_q_len=ctx.host.max_q_len)
         rec_ops.head_norm_gate(o, self.h, self.vd, self.eps, ctx.req_of_token, y, gate=z[:, 2 * hd + hv:2 * hd + 2 * hv],
                                gate_kind=rec_ops.GATE_SILU, out_scale=self.out_scale)
 
@@ -183,7 +186,7 @@ class GatedDelta(_ProjectedMixer):
             unit_heads=self.g, dim=self.d, q_scale=self.d ** -0.5, unit_eps=self.UNIT_EPS, a_raw=a_raw, a_log=self.a_log,
             dt_bias=self.dt_bias, b_raw=self._block(z, "b"))
         o = rec_ops.state_scan(conv[:, :gd], conv[:, gd:2 * gd], conv[:, 2 * gd:], cache.state, self.layout, ctx.q_start,
-                               ctx.slots, kv_heads=self.g, decay=decay, beta=beta)
+                               ctx.slots, kv_heads=self.g, decay=decay, beta=beta, max_q_len=ctx.host.max_q_len)
         if self.gate_kind == "silu":
             gate, kind = self._block(z, "g"), rec_ops.GATE_SILU
         else:
