@@ -373,8 +373,8 @@ def test_activation_and_row_additions():
 # ---- whole models -----------------------------------------------------------------------------------------------------
 
 TOL = {"float32": 1e-4, "bfloat16": 4e-2}       # relative to the largest |logit| of the request
-LENGTHS = {"A": [1, 5, 33, 70, 21, 48], "B": [2, 40, 9, 64, 17, 90], "C": [3, 37, 18, 65, 12, 30]}
-PAGE = {"A": 16, "B": 8, "C": 64}
+LENGTHS = {"A": [1, 5, 33, 70, 21, 48], "B": [2, 40, 9, 64, 17, 90], "C": [3, 37, 18, 65, 12, 30], "D": [7, 1, 50, 19, 33, 4]}
+PAGE = {"A": 16, "B": 8, "C": 64, "D": 16}
 _oracle = {}
 
 
@@ -417,7 +417,7 @@ def compare(got, want, tol, what):
                                  f"position {int(np.argmax(err > tol))} of {len(err)}")
 
 
-@pytest.mark.parametrize("which", ["A", "B", "C"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_requests_cut_four_ways_agree_with_the_plain_model(which, dtype):
     reqs, want = requests_for(which), oracle(which)

@@ -128,6 +128,10 @@ PRESETS["tirezen-tiny-C"] = _tirezen(128, 160, [
     _delta(2, 1, 128, 64, 4, 96),
     _retention(2, 64, 128, [0.96875, 0.9990234375], 64, 10000.0, 96),
     _parallel((2, 2, 64, 64, 32, 10000.0, 0.125, 20.0), (2, 2, 64, 32, 4, 16, 16), 1.2, 0.5, 96)], loop=(1, 2, 2))
+# D: no attention at all (nothing is kept in pages), every layer inside the loop, kv_heads below heads in the delta rule.
+PRESETS["tirezen-tiny-D"] = _tirezen(48, 64, [
+    _retention(3, 8, 12, [0.5, 0.9, 0.999], 4, 10.0, 32),
+    _delta(4, 1, 16, 4, 3, 40)], loop=(0, 2, 2))
 # Sizes that resemble a real model's layers (random weights, for the benchmark).
 PRESETS["tirezen-1b"] = _tirezen_stack(2048, 32000, 5, 16, 128, 8, 8192)
 PRESETS["tirezen-3b"] = _tirezen_stack(3072, 32000, 8, 24, 128, 8, 8192)
