@@ -139,7 +139,12 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* k_dst, __nv_bfloat16
 // A score in the exp2 domain: s * scale * log2(e), or with a cap c: c * tanh(s * scale / c) * log2(e).
 template <bool GEN>
 __device__ __forceinline__ float score_log2(const AttnParams& p, float s) {
-  if (GEN && p.cap_log2 > 0.f) return p.cap_log2 * tanhf(s * p.scale_over_cap);
+  if (GEN && p.cap_log2 > 0.f) {
+    // tanh(x) = 1 - 2 / (exp(2x) + 1) with the fast exponential and reciprocal: absolute error about 3e-7, which
+    // the cap multiplies to 1e-5 of a score at most (the float32 path uses tanhf in the exact kernel)
+    const float x = fminf(s * p.scale_over_cap, 15.f);
+    return p.cap_log2 * (1.0f - __fdividef(2.0f, __expf(2.0f * x) + 1.0f));
+  }
   return s * p.scale_log2;
 }
 
@@ -315,44 +320,78 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(const 
       corr[i] = exp2f(m_run[i] - base[i]);          // m_run = -inf gives 0
       m_run[i] = m_new[i];
     }
-    unsigned pf[ST / 2][4];
-    unsigned pr[GEN ? ST / 2 : 1][4];              // GEN: what the bfloat16 rounding of P left over
+    if constexpr (!GEN) {
+      unsigned pf[ST / 2][4];
 #pragma unroll
-    for (int j = 0; j < ST; ++j) {
-      const float p0 = exp2f(s[j][0] - base[0]), p1 = exp2f(s[j][1] - base[0]);
-      const float p2 = exp2f(s[j][2] - base[1]), p3 = exp2f(s[j][3] - base[1]);
-      l_add[0] += p0 + p1;
-      l_add[1] += p2 + p3;
-      pf[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);
-      pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
-      if constexpr (GEN) {
-        const float r0 = p0 - __bfloat162float(__float2bfloat16_rn(p0)), r1 = p1 - __bfloat162float(__float2bfloat16_rn(p1));
-        const float r2 = p2 - __bfloat162float(__float2bfloat16_rn(p2)), r3 = p3 - __bfloat162float(__float2bfloat16_rn(p3));
-        pr[j >> 1][(j & 1) * 2 + 0] = pack_bf16(r0, r1);
-        pr[j >> 1][(j & 1) * 2 + 1] = pack_bf16(r2, r3);
+      for (int j = 0; j < ST; ++j) {
+        const float p0 = exp2f(s[j][0] - base[0]), p1 = exp2f(s[j][1] - base[0]);
+        const float p2 = exp2f(s[j][2] - base[1]), p3 = exp2f(s[j][3] - base[1]);
+        l_add[0] += p0 + p1;
+        l_add[1] += p2 + p3;
+        pf[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);
+        pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
       }
-    }
 #pragma unroll
-    for (int i = 0; i < 2; ++i) l_run[i] = l_run[i] * corr[i] + l_add[i];
+      for (int i = 0; i < 2; ++i) l_run[i] = l_run[i] * corr[i] + l_add[i];
 #pragma unroll
-    for (int d = 0; d < DT; ++d) {
-      o[d][0] *= corr[0]; o[d][1] *= corr[0];
-      o[d][2] *= corr[1]; o[d][3] *= corr[1];
-    }
-    // ---- O += P V -------------------------------------------------------------------
+      for (int d = 0; d < DT; ++d) {
+        o[d][0] *= corr[0]; o[d][1] *= corr[0];
+        o[d][2] *= corr[1]; o[d][3] *= corr[1];
+      }
+      // ---- O += P V -------------------------------------------------------------------
 #pragma unroll
-    for (int kk = 0; kk < ST / 2; ++kk) {
+      for (int kk = 0; kk < ST / 2; ++kk) {
 #pragma unroll
-      for (int d = 0; d < DT; d += 2) {
-        unsigned vb[4];
-        const int key = wkey + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-        const int dim = d * 8 + (lane >> 4) * 8;
-        ldmatrix_x4_trans(vb, vt + key * LD + dim);
-        mma_bf16(o[d], pf[kk], vb[0], vb[1]);
-        mma_bf16(o[d + 1], pf[kk], vb[2], vb[3]);
-        if constexpr (GEN) {
-          mma_bf16(o[d], pr[kk], vb[0], vb[1]);
-          mma_bf16(o[d + 1], pr[kk], vb[2], vb[3]);
+        for (int d = 0; d < DT; d += 2) {
+          unsigned vb[4];
+          const int key = wkey + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+          const int dim = d * 8 + (lane >> 4) * 8;
+          ldmatrix_x4_trans(vb, vt + key * LD + dim);
+          mma_bf16(o[d], pf[kk], vb[0], vb[1]);
+          mma_bf16(o[d + 1], pf[kk], vb[2], vb[3]);
+        }
+      }
+    } else {
+      // The weights stay float32 in s[][]; each block of 16 keys is split into its bfloat16 rounding and the
+      // bfloat16 rounding of what that left over right before it meets V, so no second copy of P is held.
+#pragma unroll
+      for (int j = 0; j < ST; ++j) {
+        s[j][0] = exp2f(s[j][0] - base[0]); s[j][1] = exp2f(s[j][1] - base[0]);
+        s[j][2] = exp2f(s[j][2] - base[1]); s[j][3] = exp2f(s[j][3] - base[1]);
+        l_add[0] += s[j][0] + s[j][1];
+        l_add[1] += s[j][2] + s[j][3];
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i) l_run[i] = l_run[i] * corr[i] + l_add[i];
+#pragma unroll
+      for (int d = 0; d < DT; ++d) {
+        o[d][0] *= corr[0]; o[d][1] *= corr[0];
+        o[d][2] *= corr[1]; o[d][3] *= corr[1];
+      }
+#pragma unroll
+      for (int kk = 0; kk < ST / 2; ++kk) {
+        unsigned hi[4], lo[4];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const float* pv = s[2 * kk + half];
+          float r[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) r[e] = pv[e] - __bfloat162float(__float2bfloat16_rn(pv[e]));
+          hi[half * 2 + 0] = pack_bf16(pv[0], pv[1]);
+          hi[half * 2 + 1] = pack_bf16(pv[2], pv[3]);
+          lo[half * 2 + 0] = pack_bf16(r[0], r[1]);
+          lo[half * 2 + 1] = pack_bf16(r[2], r[3]);
+        }
+#pragma unroll
+        for (int d = 0; d < DT; d += 2) {
+          unsigned vb[4];
+          const int key = wkey + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+          const int dim = d * 8 + (lane >> 4) * 8;
+          ldmatrix_x4_trans(vb, vt + key * LD + dim);
+          mma_bf16(o[d], hi, vb[0], vb[1]);
+          mma_bf16(o[d + 1], hi, vb[2], vb[3]);
+          mma_bf16(o[d], lo, vb[0], vb[1]);
+          mma_bf16(o[d + 1], lo, vb[2], vb[3]);
         }
       }
     }
