@@ -11,7 +11,7 @@
 // state and the convolution's tail live in the per-request slot memory of the cache manager.
 //
 // The columns of S are independent of one another (column j only ever meets v_j), so a thread
-// owns 16 rows of one column in registers, the lanes that share a column sit in one warp, and
+// owns 8 (or 16) rows of one column in registers, the lanes that share a column sit in one warp, and
 // a block walks the tokens of one request in order: a portion of a prompt and a single
 // decoded token are the same loop, and the result for a token does not depend on how the
 // request was cut into steps or on what else is in the batch.
@@ -111,7 +111,6 @@ __global__ void short_conv_tail_kernel(const T* __restrict__ x, int x_stride, fl
 
 // ---- the recurrence ------------------------------------------------------------------------------
 constexpr int kScanThreads = 128;
-constexpr int kRows = 16;            // rows of a column a thread keeps
 constexpr int kMaxTile = 16;         // tokens staged in shared memory at a time
 
 struct ScanParams {
@@ -138,17 +137,19 @@ template <int N>
 __device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
 // DECAY: 0 constant per head, 1 scalar per token and head, 2 vector per token, head and key channel.
+// ROWS: rows of a column that a thread keeps (8: twice the warps, which hide each other's waits; 16: dim up to 512).
 // The tokens of a request are staged through two buffers in shared memory: while one tile is walked, the
 // asynchronous copies of the next are in flight.
-template <bool DELTA, int DECAY>
+template <int ROWS, bool DELTA, int DECAY>
 __global__ void __launch_bounds__(kScanThreads) state_scan_kernel(const ScanParams p) {
   extern __shared__ __align__(16) float sm[];
+  constexpr int Q = ROWS / 4;          // 16-byte pieces of a column per thread
   pdl_launch_dependents();
   pdl_wait();
   const int req = blockIdx.z, h = blockIdx.y;
   const int t_begin = p.q_start[req], q_len = p.q_start[req + 1] - t_begin;
   if (q_len <= 0) return;
-  const int L = p.lanes, cols = kScanThreads / L, width = kRows * L;
+  const int L = p.lanes, cols = kScanThreads / L, width = ROWS * L;
   const int tid = threadIdx.x, l = tid % L, c = tid / L;
   const int j = blockIdx.x * cols + c;
   const bool live = j < p.vdim;
@@ -207,15 +208,16 @@ __global__ void __launch_bounds__(kScanThreads) state_scan_kernel(const ScanPara
   };
 
   float* sp = p.state + (size_t)p.slots[req] * p.slot_stride + ((size_t)h * V + (live ? j : 0)) * Dp;
-  float S[kRows];
+  float S[ROWS];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < Q; ++i) {
     const int d = (i * L + l) * 4;
     float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
     if (live && d < Dp) x = *reinterpret_cast<const float4*>(sp + d);
     S[4 * i] = x.x; S[4 * i + 1] = x.y; S[4 * i + 2] = x.z; S[4 * i + 3] = x.w;
   }
   const float g_const = DECAY == 0 ? p.decay[h] : 1.f;
+  const bool writer = live && l == 0;
 
   issue(0, 0);
   int b = 0;
@@ -229,66 +231,67 @@ __global__ void __launch_bounds__(kScanThreads) state_scan_kernel(const ScanPara
     }
     __syncthreads();
     const float* qs = sm + (size_t)b * buf_floats;
-    const float* ks = qs + (size_t)TT * width;
-    const float* gv = ks + (size_t)TT * width;
     const float* vs = qs + (size_t)vec_cols * TT * width;
     const float* bs = vs + (size_t)TT * cols;
     const float* gs = bs + TT;
-    for (int t = 0; t < tt; ++t) {
-      float kr[kRows], qr[kRows];
+    const float* qp = qs + l * 4;                          // this lane's first piece of q; k and the decay follow
+    const float* kp = qp + (size_t)TT * width;
+    const float* gp = kp + (size_t)TT * width;
+    float* op = p.out + (size_t)(t_begin + t0) * p.out_stride + (size_t)h * V + (live ? j : 0);
+    for (int t = 0; t < tt; ++t, qp += width, kp += width, gp += width, op += p.out_stride) {
+      float kr[ROWS], qr[ROWS];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int d = (i * L + l) * 4;
-        const float4 a = *reinterpret_cast<const float4*>(ks + (size_t)t * width + d);
-        const float4 bq = *reinterpret_cast<const float4*>(qs + (size_t)t * width + d);
+      for (int i = 0; i < Q; ++i) {
+        const float4 a = *reinterpret_cast<const float4*>(kp + i * L * 4);
+        const float4 bq = *reinterpret_cast<const float4*>(qp + i * L * 4);
         kr[4 * i] = a.x; kr[4 * i + 1] = a.y; kr[4 * i + 2] = a.z; kr[4 * i + 3] = a.w;
         qr[4 * i] = bq.x; qr[4 * i + 1] = bq.y; qr[4 * i + 2] = bq.z; qr[4 * i + 3] = bq.w;
       }
       if (DECAY == 2) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float4 g = *reinterpret_cast<const float4*>(gv + (size_t)t * width + (i * L + l) * 4);
+        for (int i = 0; i < Q; ++i) {
+          const float4 g = *reinterpret_cast<const float4*>(gp + i * L * 4);
           S[4 * i] *= g.x; S[4 * i + 1] *= g.y; S[4 * i + 2] *= g.z; S[4 * i + 3] *= g.w;
         }
       } else {
         const float g = DECAY == 1 ? gs[t] : g_const;
 #pragma unroll
-        for (int r = 0; r < kRows; ++r) S[r] *= g;
+        for (int r = 0; r < ROWS; ++r) S[r] *= g;
       }
       float u = vs[t * cols + c];
       if (DELTA) {
-        // four chains of four, then a fixed tree: the order of additions is the same for every token
-        float d4[4];
+        // sums of pairs, then a fixed tree: short chains, and the same order of additions for every token
+        float part[ROWS / 2];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          d4[i] = S[4 * i] * kr[4 * i];
+        for (int i = 0; i < ROWS / 2; ++i) part[i] = __fmaf_rn(S[2 * i + 1], kr[2 * i + 1], S[2 * i] * kr[2 * i]);
 #pragma unroll
-          for (int e = 1; e < 4; ++e) d4[i] = __fmaf_rn(S[4 * i + e], kr[4 * i + e], d4[i]);
-        }
-        float dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+        for (int w = ROWS / 4; w >= 1; w >>= 1)
+#pragma unroll
+          for (int i = 0; i < w; ++i) part[i] += part[i + w];
+        float dot = part[0];
         for (int o = 1; o < L; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
         u = bs[t] * (u - dot);
       }
-      float o4[4];
+      float part[ROWS / 2];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        S[4 * i] = __fmaf_rn(kr[4 * i], u, S[4 * i]);
-        o4[i] = S[4 * i] * qr[4 * i];
-#pragma unroll
-        for (int e = 1; e < 4; ++e) {
-          S[4 * i + e] = __fmaf_rn(kr[4 * i + e], u, S[4 * i + e]);
-          o4[i] = __fmaf_rn(S[4 * i + e], qr[4 * i + e], o4[i]);
-        }
+      for (int i = 0; i < ROWS / 2; ++i) {
+        S[2 * i] = __fmaf_rn(kr[2 * i], u, S[2 * i]);
+        S[2 * i + 1] = __fmaf_rn(kr[2 * i + 1], u, S[2 * i + 1]);
+        part[i] = __fmaf_rn(S[2 * i + 1], qr[2 * i + 1], S[2 * i] * qr[2 * i]);
       }
-      float o_acc = (o4[0] + o4[1]) + (o4[2] + o4[3]);
+#pragma unroll
+      for (int w = ROWS / 4; w >= 1; w >>= 1)
+#pragma unroll
+        for (int i = 0; i < w; ++i) part[i] += part[i + w];
+      float o_acc = part[0];
       for (int o = 1; o < L; o <<= 1) o_acc += __shfl_xor_sync(0xffffffffu, o_acc, o);
-      if (live && l == 0) p.out[(size_t)(t_begin + t0 + t) * p.out_stride + (size_t)h * V + j] = o_acc;
+      if (writer) *op = o_acc;
     }
     __syncthreads();                // the next round's copies overwrite the other buffer, which the round after reads
   }
   if (live) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < Q; ++i) {
       const int d = (i * L + l) * 4;
       if (d < Dp) *reinterpret_cast<float4*>(sp + d) = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
     }
@@ -351,23 +354,36 @@ YALIS_API int yalis_delta_prepare(const void* x, int dtype, int x_stride, const 
   return YALIS_OK;
 }
 
-// Lanes that share a column of the state: the smallest power of two with 16 * lanes >= dim.
+// Rows of a column that a thread keeps: 8 up to dim 256, 16 beyond (up to 512).
+static int scan_rows(int dim) { return dim <= 256 ? 8 : 16; }
+
+// Lanes that share a column of the state: the smallest power of two with rows * lanes >= dim.
 YALIS_API int yalis_state_scan_lanes(int dim) {
   int lanes = 1;
-  while (lanes * kRows < dim) lanes <<= 1;
+  while (lanes * scan_rows(dim) < dim) lanes <<= 1;
   return lanes;
 }
 
-template <bool DELTA, int DECAY>
+template <int ROWS, bool DELTA, int DECAY>
 static int launch_scan(const ScanParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
   static size_t allowed = 48 * 1024;
   if (smem > allowed) {
-    if (cudaFuncSetAttribute(state_scan_kernel<DELTA, DECAY>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(state_scan_kernel<ROWS, DELTA, DECAY>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             200 * 1024) != cudaSuccess)
       return YALIS_ERR_LAUNCH;
     allowed = 200 * 1024;
   }
-  return yalis_launch(state_scan_kernel<DELTA, DECAY>, grid, dim3(kScanThreads), smem, stream, p);
+  return yalis_launch(state_scan_kernel<ROWS, DELTA, DECAY>, grid, dim3(kScanThreads), smem, stream, p);
+}
+
+template <int ROWS>
+static int launch_scan_rows(const ScanParams& p, dim3 grid, size_t smem, int delta, int decay_kind, cudaStream_t stream) {
+  if (delta && decay_kind == 1) return launch_scan<ROWS, true, 1>(p, grid, smem, stream);
+  if (delta && decay_kind == 2) return launch_scan<ROWS, true, 2>(p, grid, smem, stream);
+  if (delta) return launch_scan<ROWS, true, 0>(p, grid, smem, stream);
+  if (decay_kind == 0) return launch_scan<ROWS, false, 0>(p, grid, smem, stream);
+  if (decay_kind == 1) return launch_scan<ROWS, false, 1>(p, grid, smem, stream);
+  return launch_scan<ROWS, false, 2>(p, grid, smem, stream);
 }
 
 // decay_kind 0: decay [heads]; 1: decay [N, heads]; 2: decay [N, heads * dim].  beta [N, heads] with delta.
@@ -384,7 +400,8 @@ YALIS_API int yalis_state_scan(const float* q, int q_stride, const float* k, int
   if (decay_kind < 0 || decay_kind > 2 || !decay || (delta && !beta)) return YALIS_ERR_SHAPE;
   const int dim_padded = (dim + 3) & ~3;
   if ((slot_stride & 3) || ((uintptr_t)state & 15)) return YALIS_ERR_ALIGN;
-  const int cols = kScanThreads / lanes, width = kRows * lanes;
+  const int rows = scan_rows(dim);
+  const int cols = kScanThreads / lanes, width = rows * lanes;
   const size_t per_token = ((decay_kind == 2 ? 3 : 2) * (size_t)width + cols + 2) * sizeof(float);
   int tile = (int)((180 * 1024) / (2 * per_token));
   tile = tile > kMaxTile ? kMaxTile : (tile < 1 ? 1 : tile);
@@ -398,12 +415,8 @@ YALIS_API int yalis_state_scan(const float* q, int q_stride, const float* k, int
             (decay_kind != 2 || !((uintptr_t)decay & 15))) ? 1 : 0;
   const dim3 grid((vdim + cols - 1) / cols, heads, n_requests);
   const size_t smem = 2 * ((per_token * tile + 15) & ~(size_t)15);
-  if (delta && decay_kind == 1) return launch_scan<true, 1>(p, grid, smem, stream);
-  if (delta && decay_kind == 2) return launch_scan<true, 2>(p, grid, smem, stream);
-  if (delta) return launch_scan<true, 0>(p, grid, smem, stream);
-  if (decay_kind == 0) return launch_scan<false, 0>(p, grid, smem, stream);
-  if (decay_kind == 1) return launch_scan<false, 1>(p, grid, smem, stream);
-  return launch_scan<false, 2>(p, grid, smem, stream);
+  return rows == 8 ? launch_scan_rows<8>(p, grid, smem, delta, decay_kind, stream)
+                   : launch_scan_rows<16>(p, grid, smem, delta, decay_kind, stream);
 }
 
 YALIS_API int yalis_head_norm_gate(const float* o, int o_stride, const float* weight, const void* gate, int gate_stride,
