@@ -140,7 +140,8 @@ __device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_
 // ROWS: rows of a column that a thread keeps (8: twice the warps, which hide each other's waits; 16: dim up to 512).
 // The tokens of a request are staged through two buffers in shared memory: while one tile is walked, the
 // asynchronous copies of the next are in flight.
-template <int ROWS, bool DELTA, int DECAY>
+// LANES: lanes that share a column (a power of two up to 32; ROWS * LANES >= dim).
+template <int ROWS, int LANES, bool DELTA, int DECAY>
 __global__ void __launch_bounds__(kScanThreads) state_scan_kernel(const ScanParams p) {
   extern __shared__ __align__(16) float sm[];
   constexpr int Q = ROWS / 4;          // 16-byte pieces of a column per thread
@@ -149,7 +150,7 @@ __global__ void __launch_bounds__(kScanThreads) state_scan_kernel(const ScanPara
   const int req = blockIdx.z, h = blockIdx.y;
   const int t_begin = p.q_start[req], q_len = p.q_start[req + 1] - t_begin;
   if (q_len <= 0) return;
-  const int L = p.lanes, cols = kScanThreads / L, width = ROWS * L;
+  constexpr int L = LANES, cols = kScanThreads / L, width = ROWS * L;
   const int tid = threadIdx.x, l = tid % L, c = tid / L;
   const int j = blockIdx.x * cols + c;
   const bool live = j < p.vdim;
@@ -269,6 +270,7 @@ __global__ void __launch_bounds__(kScanThreads) state_scan_kernel(const ScanPara
 #pragma unroll
           for (int i = 0; i < w; ++i) part[i] += part[i + w];
         float dot = part[0];
+#pragma unroll
         for (int o = 1; o < L; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
         u = bs[t] * (u - dot);
       }
@@ -284,6 +286,7 @@ __global__ void __launch_bounds__(kScanThreads) state_scan_kernel(const ScanPara
 #pragma unroll
         for (int i = 0; i < w; ++i) part[i] += part[i + w];
       float o_acc = part[0];
+#pragma unroll
       for (int o = 1; o < L; o <<= 1) o_acc += __shfl_xor_sync(0xffffffffu, o_acc, o);
       if (writer) *op = o_acc;
     }
@@ -364,26 +367,26 @@ YALIS_API int yalis_state_scan_lanes(int dim) {
   return lanes;
 }
 
-template <int ROWS, bool DELTA, int DECAY>
+template <int ROWS, int LANES, bool DELTA, int DECAY>
 static int launch_scan(const ScanParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
   static size_t allowed = 48 * 1024;
   if (smem > allowed) {
-    if (cudaFuncSetAttribute(state_scan_kernel<ROWS, DELTA, DECAY>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(state_scan_kernel<ROWS, LANES, DELTA, DECAY>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              200 * 1024) != cudaSuccess)
       return YALIS_ERR_LAUNCH;
     allowed = 200 * 1024;
   }
-  return yalis_launch(state_scan_kernel<ROWS, DELTA, DECAY>, grid, dim3(kScanThreads), smem, stream, p);
+  return yalis_launch(state_scan_kernel<ROWS, LANES, DELTA, DECAY>, grid, dim3(kScanThreads), smem, stream, p);
 }
 
-template <int ROWS>
-static int launch_scan_rows(const ScanParams& p, dim3 grid, size_t smem, int delta, int decay_kind, cudaStream_t stream) {
-  if (delta && decay_kind == 1) return launch_scan<ROWS, true, 1>(p, grid, smem, stream);
-  if (delta && decay_kind == 2) return launch_scan<ROWS, true, 2>(p, grid, smem, stream);
-  if (delta) return launch_scan<ROWS, true, 0>(p, grid, smem, stream);
-  if (decay_kind == 0) return launch_scan<ROWS, false, 0>(p, grid, smem, stream);
-  if (decay_kind == 1) return launch_scan<ROWS, false, 1>(p, grid, smem, stream);
-  return launch_scan<ROWS, false, 2>(p, grid, smem, stream);
+template <int ROWS, int LANES>
+static int launch_scan_kind(const ScanParams& p, dim3 grid, size_t smem, int delta, int decay_kind, cudaStream_t stream) {
+  if (delta && decay_kind == 1) return launch_scan<ROWS, LANES, true, 1>(p, grid, smem, stream);
+  if (delta && decay_kind == 2) return launch_scan<ROWS, LANES, true, 2>(p, grid, smem, stream);
+  if (delta) return launch_scan<ROWS, LANES, true, 0>(p, grid, smem, stream);
+  if (decay_kind == 0) return launch_scan<ROWS, LANES, false, 0>(p, grid, smem, stream);
+  if (decay_kind == 1) return launch_scan<ROWS, LANES, false, 1>(p, grid, smem, stream);
+  return launch_scan<ROWS, LANES, false, 2>(p, grid, smem, stream);
 }
 
 // decay_kind 0: decay [heads]; 1: decay [N, heads]; 2: decay [N, heads * dim].  beta [N, heads] with delta.
@@ -415,8 +418,15 @@ YALIS_API int yalis_state_scan(const float* q, int q_stride, const float* k, int
             (decay_kind != 2 || !((uintptr_t)decay & 15))) ? 1 : 0;
   const dim3 grid((vdim + cols - 1) / cols, heads, n_requests);
   const size_t smem = 2 * ((per_token * tile + 15) & ~(size_t)15);
-  return rows == 8 ? launch_scan_rows<8>(p, grid, smem, delta, decay_kind, stream)
-                   : launch_scan_rows<16>(p, grid, smem, delta, decay_kind, stream);
+  if (rows == 16) return launch_scan_kind<16, 32>(p, grid, smem, delta, decay_kind, stream);
+  switch (lanes) {
+    case 1: return launch_scan_kind<8, 1>(p, grid, smem, delta, decay_kind, stream);
+    case 2: return launch_scan_kind<8, 2>(p, grid, smem, delta, decay_kind, stream);
+    case 4: return launch_scan_kind<8, 4>(p, grid, smem, delta, decay_kind, stream);
+    case 8: return launch_scan_kind<8, 8>(p, grid, smem, delta, decay_kind, stream);
+    case 16: return launch_scan_kind<8, 16>(p, grid, smem, delta, decay_kind, stream);
+    default: return launch_scan_kind<8, 32>(p, grid, smem, delta, decay_kind, stream);
+  }
 }
 
 YALIS_API int yalis_head_norm_gate(const float* o, int o_stride, const float* weight, const void* gate, int gate_stride,
