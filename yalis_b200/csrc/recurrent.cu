@@ -159,6 +159,9 @@ __global__ void __launch_bounds__(kScanThreads) state_scan_kernel(const ScanPara
   // one buffer: q [TT][width], k [TT][width], decay vectors [TT][width] (DECAY 2), v [TT][cols], beta [TT], decay [TT]
   const size_t buf_floats = ((size_t)(DECAY == 2 ? 3 : 2) * TT * width + (size_t)TT * cols + 2 * TT + 3) & ~(size_t)3;
   const int vec_cols = DECAY == 2 ? 3 : 2;
+  // behind the two buffers: every lane's share of a read-out, [TT][cols][L + 1]; the shares are added after the
+  // tile is walked, off the chain from one token's state to the next
+  float* shares = sm + 2 * buf_floats;
 
   // what no copy ever writes: the rows past dim (zeros; ones for the decay)
   const int pad = width - D;
@@ -218,7 +221,6 @@ __global__ void __launch_bounds__(kScanThreads) state_scan_kernel(const ScanPara
     S[4 * i] = x.x; S[4 * i + 1] = x.y; S[4 * i + 2] = x.z; S[4 * i + 3] = x.w;
   }
   const float g_const = DECAY == 0 ? p.decay[h] : 1.f;
-  const bool writer = live && l == 0;
 
   issue(0, 0);
   int b = 0;
@@ -238,8 +240,7 @@ __global__ void __launch_bounds__(kScanThreads) state_scan_kernel(const ScanPara
     const float* qp = qs + l * 4;                          // this lane's first piece of q; k and the decay follow
     const float* kp = qp + (size_t)TT * width;
     const float* gp = kp + (size_t)TT * width;
-    float* op = p.out + (size_t)(t_begin + t0) * p.out_stride + (size_t)h * V + (live ? j : 0);
-    for (int t = 0; t < tt; ++t, qp += width, kp += width, gp += width, op += p.out_stride) {
+    for (int t = 0; t < tt; ++t, qp += width, kp += width, gp += width) {
       float kr[ROWS], qr[ROWS];
 #pragma unroll
       for (int i = 0; i < Q; ++i) {
@@ -285,12 +286,18 @@ __global__ void __launch_bounds__(kScanThreads) state_scan_kernel(const ScanPara
       for (int w = ROWS / 4; w >= 1; w >>= 1)
 #pragma unroll
         for (int i = 0; i < w; ++i) part[i] += part[i + w];
-      float o_acc = part[0];
-#pragma unroll
-      for (int o = 1; o < L; o <<= 1) o_acc += __shfl_xor_sync(0xffffffffu, o_acc, o);
-      if (writer) *op = o_acc;
+      shares[(t * cols + c) * (L + 1) + l] = part[0];
     }
     __syncthreads();                // the next round's copies overwrite the other buffer, which the round after reads
+    for (int e = tid; e < tt * cols; e += kScanThreads) {
+      const int t = e / cols, cc = e - t * cols;
+      const int jj = blockIdx.x * cols + cc;
+      const float* sh = shares + (size_t)e * (L + 1);
+      float o_acc = sh[0];
+#pragma unroll
+      for (int i = 1; i < L; ++i) o_acc += sh[i];          // lane order: the same sum for every token
+      if (jj < V) p.out[(size_t)(t_begin + t0 + t) * p.out_stride + (size_t)h * V + jj] = o_acc;
+    }
   }
   if (live) {
 #pragma unroll
@@ -417,7 +424,7 @@ YALIS_API int yalis_state_scan(const float* q, int q_stride, const float* k, int
   p.wide = (dim % 4 == 0 && q_stride % 4 == 0 && k_stride % 4 == 0 && !((uintptr_t)q & 15) && !((uintptr_t)k & 15) &&
             (decay_kind != 2 || !((uintptr_t)decay & 15))) ? 1 : 0;
   const dim3 grid((vdim + cols - 1) / cols, heads, n_requests);
-  const size_t smem = 2 * ((per_token * tile + 15) & ~(size_t)15);
+  const size_t smem = 2 * ((per_token * tile + 15) & ~(size_t)15) + (size_t)tile * cols * (lanes + 1) * sizeof(float);
   if (rows == 16) return launch_scan_kind<16, 32>(p, grid, smem, delta, decay_kind, stream);
   switch (lanes) {
     case 1: return launch_scan_kind<8, 1>(p, grid, smem, delta, decay_kind, stream);
