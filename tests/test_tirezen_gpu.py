@@ -118,7 +118,7 @@ def plain_scan(q, k, v, heads, kv_heads, decay, beta=None):
 @pytest.mark.parametrize("mode, heads, kv_heads, D, V", [
     ("retention", 2, 2, 16, 24), ("retention", 1, 1, 40, 8), ("head", 4, 2, 12, 20), ("head", 3, 3, 6, 10),
     ("head", 2, 1, 128, 64), ("channel", 4, 2, 8, 16), ("channel", 2, 1, 20, 6), ("channel", 2, 2, 64, 130),
-    ("head", 1, 1, 200, 32), ("plain_channel", 2, 2, 10, 12),
+    ("head", 1, 1, 200, 32), ("plain_channel", 2, 2, 10, 12), ("channel", 1, 1, 300, 8), ("retention", 2, 1, 130, 5),
 ])
 def test_state_scan_against_the_plain_recurrence_however_the_tokens_are_cut(mode, heads, kv_heads, D, V):
     from yalis_b200.ops.recurrent import StateLayout, state_scan
