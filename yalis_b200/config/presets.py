@@ -132,6 +132,12 @@ PRESETS["tirezen-tiny-C"] = _tirezen(128, 160, [
 PRESETS["tirezen-tiny-D"] = _tirezen(48, 64, [
     _retention(3, 8, 12, [0.5, 0.9, 0.999], 4, 10.0, 32),
     _delta(4, 1, 16, 4, 3, 40)], loop=(0, 2, 2))
+# E: a width and head sizes that are multiples of 2 or 3 only (no row starts on a 16-byte boundary), attention whose
+# keys and values share a head size of 16 (the tensor-core kernel's smallest), six taps.
+PRESETS["tirezen-tiny-E"] = _tirezen(36, 37, [
+    _parallel((2, 1, 16, 16, 10, 300.0, 0.4, 8.0), (3, 3, 9, 3, 6, 3, 7), 0.9, 1.1, 30),
+    _retention(2, 10, 7, [0.8, 0.95], 6, 50.0, None),
+    _delta(2, 2, 5, 9, 6, 22)], loop=(1, 3, 2))
 # Sizes that resemble a real model's layers (random weights, for the benchmark).
 PRESETS["tirezen-1b"] = _tirezen_stack(2048, 32000, 5, 16, 128, 8, 8192)
 PRESETS["tirezen-3b"] = _tirezen_stack(3072, 32000, 8, 24, 128, 8, 8192)
