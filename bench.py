@@ -30,7 +30,7 @@ tokens per second of the whole call.  For these, ``--warmup`` and ``--steps`` co
 calls (defaults 2 and 3; the median call is reported).
 
 ``--workload mixers``: for each size, the Tirezen preset (layers of delta rule, attention beside a
-delta rule, and retention) and the Llama preset of the same width: a 2,048-token prefill and decode
+delta rule, and retention) and the Llama preset of the same width: a 2,048-token prefill (also four such prompts in one step) and decode
 steps at batch 8 and 64 after 1,024-token prompts, each with its fraction of the roofline (prefill:
 matrix and mixing flops over the measured bf16 peak; decode: weights, keys and per-request state
 over the measured copy bandwidth).  ``value`` is Tirezen's decode tokens per second at batch 8 of
@@ -292,14 +292,18 @@ def run_mixers(args) -> int:
                             InferenceConfig(max_batch_size=max(batches), max_length_of_generated_sequences=max(max_len, PREFILL_TOKENS + 64),
                                             temperature=0.0, top_p=0.0, page_size=args.page_size,
                                             cache_tokens=max(batches) * (max_len + args.page_size),
-                                            max_tokens_per_step=max(PREFILL_TOKENS, 8 * PROMPT_LEN)))
+                                            max_tokens_per_step=max(4 * PREFILL_TOKENS, 8 * PROMPT_LEN)))
             engine = llm.engine
             numbers = model_numbers(engine)
             pf = prefill_bench(engine, PREFILL_TOKENS, warmup=3, iters=5)
             flops = numbers["flops_prefill"](PREFILL_TOKENS)
+            pf4 = prefill_bench(engine, PREFILL_TOKENS, warmup=2, iters=3, prompts=4)
             rec = {"weights_gb": round(numbers["weight_bytes_per_step"] / 1e9, 3),
                    "prefill": {"tokens": PREFILL_TOKENS, "ms": round(pf, 3), "tok_s": round(PREFILL_TOKENS / (pf / 1e3), 1),
-                               "frac_of_bf16_peak": round(flops / (pf / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)}}
+                               "frac_of_bf16_peak": round(flops / (pf / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)},
+                   "prefill_4_prompts": {"tokens": 4 * PREFILL_TOKENS, "ms": round(pf4, 3),
+                                         "tok_s": round(4 * PREFILL_TOKENS / (pf4 / 1e3), 1),
+                                         "frac_of_bf16_peak": round(4 * flops / (pf4 / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)}}
             for b in batches:
                 bench = DecodeBench(engine, b, PROMPT_LEN, seed=b)
                 bench.prepare()

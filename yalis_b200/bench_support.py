@@ -138,22 +138,24 @@ class DecodeBench:
         self.slots = []
 
 
-def prefill_bench(engine: Engine, tokens: int, warmup: int = 2, iters: int = 3) -> float:
-    """Milliseconds (median of ``iters``) of one step that prefills a single ``tokens``-token prompt (logits of
-    its last token)."""
+def prefill_bench(engine: Engine, tokens: int, warmup: int = 2, iters: int = 3, prompts: int = 1) -> float:
+    """Milliseconds (median of ``iters``) of one step that prefills ``prompts`` prompts of ``tokens`` tokens each
+    (logits of their last tokens)."""
     gen = torch.Generator().manual_seed(7)
-    prompt = torch.randint(0, engine.vocab_size, (tokens,), generator=gen).tolist()
+    texts = [torch.randint(0, engine.vocab_size, (tokens,), generator=gen).tolist() for _ in range(prompts)]
     times = []
     for i in range(warmup + iters):
-        rid = ("prefill", i)
-        engine.add_request(rid)
+        rids = [("prefill", i, j) for j in range(prompts)]
+        for rid in rids:
+            engine.add_request(rid)
         torch.cuda.synchronize()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
-        engine.step([StepEntry(rid, prompt, [tokens - 1])])
+        engine.step([StepEntry(rid, text, [tokens - 1]) for rid, text in zip(rids, texts)])
         end.record()
         torch.cuda.synchronize()
-        engine.finish_request(rid)
+        for rid in rids:
+            engine.finish_request(rid)
         if i >= warmup:
             times.append(start.elapsed_time(end))
     times.sort()
