@@ -2,6 +2,8 @@
 
     python profile_cases.py attention_decode --batch 64 --ctx 1040 --launches 8
     python profile_cases.py gemm_wstream --tokens 8 --n 28672 --k 4096 --launches 8
+    python profile_cases.py recurrence --requests 1 --tokens 2048        # the state-keeping mixers' kernels
+    python profile_cases.py prefill --preset tirezen-1b --layers 3 --tokens 2048
 
 Each case allocates inputs larger than the L2 cache but at most a few GB, launches the
 kernel a few times, and prints the mean time per launch measured with CUDA events.
@@ -219,13 +221,81 @@ def prefill(args) -> None:
     from yalis_b200.config.presets import preset
     from yalis_b200.engine.engine import Engine
     cfg = preset(args.preset)
-    if args.layers:
+    if args.layers and "num_hidden_layers" in cfg:
         cfg["num_hidden_layers"] = args.layers
+    elif args.layers:                         # a configuration that lists its layers
+        cfg["layers"] = cfg["layers"][:args.layers]
+    n_layers = cfg.get("num_hidden_layers") or len(cfg["layers"])
     engine = Engine(config=cfg, seed=0, dtype=args.dtype, page_size=64, cache_tokens=args.tokens + 64, max_slots=2,
                     max_context=args.tokens + 64)
-    ms = prefill_bench(engine, args.tokens, warmup=1, iters=args.launches)
-    print(f"prefill {args.preset} layers {cfg['num_hidden_layers']} tokens {args.tokens} {args.dtype}: {ms:.3f} ms, "
+    ms = prefill_bench(engine, args.tokens, warmup=3, iters=args.launches)
+    print(f"prefill {args.preset} layers {n_layers} tokens {args.tokens} {args.dtype}: {ms:.3f} ms, "
           f"{args.tokens / ms * 1e3:.0f} tokens/s")
+
+
+def recurrence(args) -> None:
+    """The kernels of the state-keeping mixers at one layer's shape: ``--requests`` requests of ``--tokens`` tokens each
+    (1 token: a decode step).  Launched one by one with the L2 written over between launches; median of ``--launches``."""
+    from yalis_b200.ops import attention as A, recurrent as R
+    dev = "cuda:0"
+    h, g, d, v, n_req, per = args.heads, args.kv_heads, args.head_dim, args.head_dim, args.requests, args.tokens
+    n = n_req * per
+    flush = torch.empty(64 * 1024 * 1024, device=dev)
+
+    def timed(fn):
+        times = []
+        for i in range(3 + args.launches):
+            flush.zero_()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                times.append(a.elapsed_time(b) * 1e3)
+        return sorted(times)[len(times) // 2]
+
+    def i32(x):
+        return torch.tensor(list(x), dtype=torch.int32, device=dev)
+
+    qs, slots = i32(i * per for i in range(n_req + 1)), i32(range(n_req))
+    req = i32(i // per for i in range(n))
+    pos = i32((i % per) + (args.cached if per == 1 else 0) for i in range(n))
+    lay = R.StateLayout(h, d, v, 2 * g * d + h * v, 4)
+    rows = torch.zeros(n_req + 1, lay.total, device=dev)
+    q, k = torch.randn(n, g * d, device=dev) * 0.05, torch.randn(n, g * d, device=dev) * 0.05
+    qh, kh = torch.randn(n, h * d, device=dev) * 0.05, torch.randn(n, h * d, device=dev) * 0.05
+    val = torch.randn(n, h * v, device=dev)
+    beta, per_head = torch.rand(n, h, device=dev), torch.rand(n, h, device=dev) * 0.1 + 0.9
+    per_channel, const = torch.rand(n, h * d, device=dev) * 0.1 + 0.9, torch.full((h,), 0.99, device=dev)
+    lay_r = R.StateLayout(h, d, v)
+    rows_r = torch.zeros(n_req + 1, lay_r.total, device=dev)
+    out = {
+        "state_scan delta rule, decay per head": timed(lambda: R.state_scan(q, k, val, rows, lay, qs, slots, kv_heads=g, decay=per_head, beta=beta, max_q_len=per)),
+        "state_scan delta rule, decay per channel": timed(lambda: R.state_scan(q, k, val, rows, lay, qs, slots, kv_heads=g, decay=per_channel, beta=beta, max_q_len=per)),
+        "state_scan retention": timed(lambda: R.state_scan(qh, kh, val, rows_r, lay_r, qs, slots, kv_heads=h, decay=const, max_q_len=per)),
+    }
+    c = 2 * g * d + h * v
+    z = torch.randn(n, c + h * v + 2 * h, device=dev).to(torch.bfloat16)
+    w, zeros = torch.randn(c, 4, device=dev), torch.zeros(h, device=dev)
+    out["delta_prepare"] = timed(lambda: R.delta_prepare(z[:, :c], w, rows, lay.state_floats, req, qs, slots, unit_heads=g, dim=d,
+                                                         q_scale=d ** -0.5, a_raw=z[:, c + h * v:c + h * v + h], a_log=zeros,
+                                                         dt_bias=zeros, b_raw=z[:, c + h * v + h:c + h * v + 2 * h]))
+    o, y = torch.randn(n, h * v, device=dev), torch.empty(n, h * v, device=dev, dtype=torch.bfloat16)
+    out["head_norm_gate"] = timed(lambda: R.head_norm_gate(o, h, v, 1e-5, req, y, weight=torch.ones(v, device=dev), gate=z[:, c:c + h * v], gate_kind=1))
+    page, ctx = 64, (per if per > 1 else args.cached + 1)
+    pages = -(-ctx // page)
+    kp = torch.randn(n_req * pages + 1, g, page, d, device=dev).to(torch.bfloat16)
+    vp = torch.randn(n_req * pages + 1, g, page, d, device=dev).to(torch.bfloat16)
+    table = torch.arange(n_req * pages, dtype=torch.int32, device=dev).reshape(n_req, pages)
+    qa = (torch.randn(n, h * d, device=dev) * 0.1).to(torch.bfloat16)
+    splits = A.decode_splits(n_req, g) if per * (h // g) <= 16 else 1
+    out["attention, general form (cap, sink, split weights)"] = timed(lambda: A.paged_attention_mma(
+        qa, kp, vp, pos, qs, req, table, per, h, g, d, n_splits=splits, softcap=30.0, sink=True, exact_weights=True))
+    out["attention, plain form"] = timed(lambda: A.paged_attention_mma(qa, kp, vp, pos, qs, req, table, per, h, g, d, n_splits=splits))
+    for name, us in out.items():
+        print(f"{name}: {us:.1f} us  ({n_req} x {per} tokens, {h} heads / {g} KV heads x {d})")
 
 
 def main() -> None:
@@ -281,6 +351,15 @@ def main() -> None:
     pf.add_argument("--dtype", default="bfloat16")
     pf.add_argument("--launches", type=int, default=2)
     pf.set_defaults(fn=prefill)
+    rc = sub.add_parser("recurrence")
+    rc.add_argument("--requests", type=int, default=1)
+    rc.add_argument("--tokens", type=int, default=2048, help="tokens each request brings (1: a decode step)")
+    rc.add_argument("--cached", type=int, default=1024, help="tokens each request holds already when it brings one")
+    rc.add_argument("--heads", type=int, default=16)
+    rc.add_argument("--kv-heads", type=int, default=8)
+    rc.add_argument("--head-dim", type=int, default=128)
+    rc.add_argument("--launches", type=int, default=10)
+    rc.set_defaults(fn=recurrence)
     args = ap.parse_args()
     args.fn(args)
 
