@@ -123,11 +123,11 @@ PRESETS["tirezen-tiny-A"] = _tirezen(64, 96, [
 PRESETS["tirezen-tiny-B"] = _tirezen(40, 50, [
     _delta(3, 3, 6, 10, 5, 24),
     _parallel((3, 1, 20, 36, 20, 500.0, 0.2, 30.0), (2, 1, 20, 6, 4, 5, 12), 1.0, 0.25, None),
-    _retention(1, 40, 8, [0.99], 16, 1000000.0, 56)], eps=1e-6)
+    _retention(1, 40, 8, [0.99], 16, 200000.0, 56)], eps=1e-6)
 PRESETS["tirezen-tiny-C"] = _tirezen(128, 160, [
     _delta(2, 1, 128, 64, 4, 96),
-    _retention(2, 64, 128, [0.96875, 0.9990234375], 64, 10000.0, 96),
-    _parallel((2, 2, 64, 64, 32, 10000.0, 0.125, 20.0), (2, 2, 64, 32, 4, 16, 16), 1.2, 0.5, 96)], loop=(1, 2, 2))
+    _retention(2, 64, 128, [0.97, 0.995], 64, 10000.0, 96),
+    _parallel((2, 2, 64, 64, 32, 10000.0, 0.125, 25.0), (2, 2, 64, 48, 4, 16, 16), 1.1, 0.6, 96)], loop=(1, 2, 2))
 # D: no attention at all (nothing is kept in pages), every layer inside the loop, kv_heads below heads in the delta rule.
 PRESETS["tirezen-tiny-D"] = _tirezen(48, 64, [
     _retention(3, 8, 12, [0.5, 0.9, 0.999], 4, 10.0, 32),
