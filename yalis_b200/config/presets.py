@@ -109,7 +109,7 @@ def _tirezen_stack(width, vocab, groups, heads, dim, kv_heads, ff) -> Dict[str, 
         layers.append(_delta(heads, kv_heads, dim, dim, 4, ff))
         layers.append(_parallel((heads, kv_heads, dim, dim, dim, 10000.0, dim ** -0.5, 30.0),
                                 (heads, kv_heads, dim, dim, 4, 64, 64), 1.0, 1.0, ff))
-        layers.append(_retention(heads, dim, dim, [1.0 - 2.0 ** (-5 - (i % 4)) for i in range(heads)], dim, 10000.0, ff))
+        layers.append(_retention(heads, dim, dim, [1.0 - 0.04 / (1 + i % 4) for i in range(heads)], dim, 10000.0, ff))
     return _tirezen(width, vocab, layers)
 
 
