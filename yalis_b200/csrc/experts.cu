@@ -1,0 +1,385 @@
+// A routed feed-forward (mixture of experts): every token runs `top` of E small feed-forwards and adds their
+// results with weights from a router.
+//
+//   route_topk     scores = softmax(logits) over all experts (float32), the `top` largest, their scores divided
+//                  by their sum (+ eps); ties go to the smaller index.
+//   expert_plan    sorts the (token, choice) entries by expert: offsets per expert, a permutation slot -> entry and
+//                  its inverse, and the list of row tiles (expert, first slot) that the products walk.  The order
+//                  of entries inside an expert is whatever the atomics give; no result depends on it, since every
+//                  entry's rows are computed on their own and added per token in the order of the choices.
+//   grouped_gemm   C[slot, :] = act(A[row(slot), :] . W[expert(slot)]^T): one launch for all experts, a block per
+//                  (row tile, column tile); blocks past the last tile leave.  bfloat16 on mma.sync tensor cores
+//                  with float32 accumulators, float32 on the CUDA cores in k order.
+//   expert_combine out[n, :] = sum_j weight[n, j] * Y[slot(n, j), :] (+ shared[n, :]), float32, in the order of j.
+//
+// Nothing here synchronises with the host or sizes a launch by the routing, so a step with routed layers can
+// be recorded and replayed.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kMaxExperts = 1024;
+constexpr int kMaxTop = 32;
+
+// One warp per token.
+__global__ void route_topk_kernel(const float* __restrict__ logits, int E, int top, float eps,
+                                  const int32_t* __restrict__ req_of_token, int32_t* __restrict__ ids,
+                                  float* __restrict__ weights, int n_tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (n >= n_tokens) return;
+  if (req_of_token && req_of_token[n] < 0) {
+    for (int j = lane; j < top; j += 32) {
+      ids[(size_t)n * top + j] = -1;
+      weights[(size_t)n * top + j] = 0.f;
+    }
+    return;
+  }
+  constexpr int kPer = kMaxExperts / 32;
+  float s[kPer];
+  const float* z = logits + (size_t)n * E;
+  float m = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) {
+    const int e = lane + 32 * i;
+    s[i] = e < E ? z[e] : -INFINITY;
+    m = fmaxf(m, s[i]);
+  }
+  m = warp_max(m);
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) {
+    s[i] = (lane + 32 * i) < E ? expf(s[i] - m) : -1.f;    // -1: not an expert, never chosen
+    if (s[i] > 0.f) sum += s[i];
+  }
+  sum = warp_sum(sum);
+#pragma unroll
+  for (int i = 0; i < kPer; ++i)
+    if (s[i] >= 0.f) s[i] = s[i] / sum;
+  float chosen_w = 0.f, total = 0.f;     // lane j keeps the j-th choice
+  int chosen_e = -1;
+  for (int j = 0; j < top; ++j) {
+    float best = -1.f;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i)
+      if (s[i] > best) {                 // ascending e within a lane: the first maximum is the smallest index
+        best = s[i];
+        best_e = lane + 32 * i;
+      }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) {
+        best = ob;
+        best_e = oe;
+      }
+    }
+    if ((best_e & 31) == lane) {
+#pragma unroll
+      for (int i = 0; i < kPer; ++i)
+        if (lane + 32 * i == best_e) s[i] = -1.f;
+    }
+    if (lane == j) {
+      chosen_w = best;
+      chosen_e = best_e;
+    }
+    total += best;                       // the same on every lane, in the order of the choices
+  }
+  if (lane < top) {
+    ids[(size_t)n * top + lane] = chosen_e;
+    weights[(size_t)n * top + lane] = chosen_w / (total + eps);
+  }
+}
+
+// One block.  entries = n_tokens * top.  tiles: (expert, first slot) per row tile of `bm` slots, ended by n_tiles.
+__global__ void expert_plan_kernel(const int32_t* __restrict__ ids, int entries, int E, int bm, int32_t* __restrict__ offsets,
+                                   int32_t* __restrict__ perm, int32_t* __restrict__ inv, int32_t* __restrict__ tile_expert,
+                                   int32_t* __restrict__ tile_slot, int32_t* __restrict__ n_tiles) {
+  __shared__ int count[kMaxExperts], start[kMaxExperts + 1], tile0[kMaxExperts + 1];
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < entries; i += blockDim.x) {
+    const int e = ids[i];
+    if (e >= 0 && e < E) atomicAdd(&count[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      start[e] = at;
+      tile0[e] = tiles;
+      at += count[e];
+      tiles += (count[e] + bm - 1) / bm;
+    }
+    start[E] = at;
+    tile0[E] = tiles;
+    *n_tiles = tiles;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = start[e];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int nt = tile0[e + 1] - tile0[e];
+    for (int t = 0; t < nt; ++t) {
+      tile_expert[tile0[e] + t] = e;
+      tile_slot[tile0[e] + t] = start[e] + t * bm;
+    }
+    count[e] = 0;      // now the cursor
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < entries; i += blockDim.x) {
+    const int e = ids[i];
+    if (e >= 0 && e < E) {
+      const int slot = start[e] + atomicAdd(&count[e], 1);
+      perm[slot] = i;
+      inv[i] = slot;
+    } else {
+      inv[i] = -1;
+    }
+  }
+}
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+  if (act == 1) {            // the square of relu
+    v = fmaxf(v, 0.f);
+    return v * v;
+  }
+  return v;
+}
+
+struct GroupedArgs {
+  const void* a; long a_stride;       // [rows, K]
+  const int32_t* perm; int top;       // row of slot s: perm[s] / top (perm null: the slot itself)
+  const void* w;                      // [E, n_out, K]
+  void* c; long c_stride;             // [slots, n_out]
+  const int32_t* offsets; const int32_t* tile_expert; const int32_t* tile_slot; const int32_t* n_tiles;
+  int n_out, K, act;
+};
+
+// float32 (or any dtype without alignment demands): 32 x 64 tile, 256 threads, 2 x 4 outputs a thread.
+template <typename T>
+__global__ void grouped_gemm_simt_kernel(const GroupedArgs g) {
+  constexpr int BM = 32, BN = 64, BK = 16;
+  __shared__ float As[BM][BK + 1], Bs[BN][BK + 1];
+  __shared__ int rows[BM];
+  pdl_launch_dependents();
+  pdl_wait();
+  if ((int)blockIdx.x >= *g.n_tiles) return;
+  const int e = g.tile_expert[blockIdx.x], slot0 = g.tile_slot[blockIdx.x];
+  const int m_rows = min(BM, g.offsets[e + 1] - slot0);
+  const int n0 = blockIdx.y * BN;
+  const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+  if (tid < BM) rows[tid] = tid < m_rows ? (g.perm ? g.perm[slot0 + tid] / g.top : slot0 + tid) : -1;
+  __syncthreads();
+  const T* A = reinterpret_cast<const T*>(g.a);
+  const T* W = reinterpret_cast<const T*>(g.w) + (size_t)e * g.n_out * g.K;
+  float acc[2][4] = {};
+  for (int k0 = 0; k0 < g.K; k0 += BK) {
+    for (int i = tid; i < BM * BK; i += 256) {
+      const int r = i / BK, k = i % BK;
+      As[r][k] = (rows[r] >= 0 && k0 + k < g.K) ? to_f32<T>(A[(size_t)rows[r] * g.a_stride + k0 + k]) : 0.f;
+    }
+    for (int i = tid; i < BN * BK; i += 256) {
+      const int r = i / BK, k = i % BK;
+      Bs[r][k] = (n0 + r < g.n_out && k0 + k < g.K) ? to_f32<T>(W[(size_t)(n0 + r) * g.K + k0 + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < BK; ++k) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = __fmaf_rn(As[ty * 2 + i][k], Bs[tx + 16 * j][k], acc[i][j]);
+    }
+    __syncthreads();
+  }
+  T* C = reinterpret_cast<T*>(g.c);
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = ty * 2 + i;
+    if (r >= m_rows) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int c = n0 + tx + 16 * j;
+      if (c < g.n_out) C[(size_t)(slot0 + r) * g.c_stride + c] = from_f32<T>(apply_act(acc[i][j], g.act));
+    }
+  }
+}
+
+// bfloat16 on mma.sync.m16n8k16: BM x 64 tile, 4 warps, K in steps of 32 through a two-stage cp.async ring.
+// BM = 32: warps side by side along the columns (16 each); BM = 128: warps stacked along the rows (32 each).
+// Needs K % 8 == 0 and 16-byte aligned rows of A and W.
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(bytes) : "memory");
+}
+
+template <int BM>
+__global__ void __launch_bounds__(128) grouped_gemm_mma_kernel(const GroupedArgs g) {
+  constexpr int BN = 64, BK = 32, LD = BK + 8;          // rows of 80 bytes: fragment loads hit 32 distinct banks
+  constexpr int WARPS_M = BM / 32, WARPS_N = 4 / WARPS_M, WN = BN / WARPS_N, NT = WN / 8;
+  __shared__ __align__(16) __nv_bfloat16 As[2][BM][LD];
+  __shared__ __align__(16) __nv_bfloat16 Bs[2][BN][LD];
+  __shared__ int rows[BM];
+  pdl_launch_dependents();
+  pdl_wait();
+  if ((int)blockIdx.x >= *g.n_tiles) return;
+  const int e = g.tile_expert[blockIdx.x], slot0 = g.tile_slot[blockIdx.x];
+  const int m_rows = min(BM, g.offsets[e + 1] - slot0);
+  const int n0 = blockIdx.y * BN;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int wm = warp / WARPS_N, wn = warp % WARPS_N;
+  for (int i = tid; i < BM; i += 128) rows[i] = i < m_rows ? (g.perm ? g.perm[slot0 + i] / g.top : slot0 + i) : -1;
+  __syncthreads();
+  const __nv_bfloat16* A = reinterpret_cast<const __nv_bfloat16*>(g.a);
+  const __nv_bfloat16* W = reinterpret_cast<const __nv_bfloat16*>(g.w) + (size_t)e * g.n_out * g.K;
+
+  auto load = [&](int stage, int k0) {
+    for (int i = tid; i < BM * 4; i += 128) {
+      const int r = i >> 2, ch = i & 3;
+      const bool ok = rows[r] >= 0 && k0 + ch * 8 < g.K;
+      cp_async16(&As[stage][r][ch * 8], ok ? A + (size_t)rows[r] * g.a_stride + k0 + ch * 8 : A, ok);
+    }
+    for (int i = tid; i < BN * 4; i += 128) {
+      const int r = i >> 2, ch = i & 3;
+      const bool ok = n0 + r < g.n_out && k0 + ch * 8 < g.K;
+      cp_async16(&Bs[stage][r][ch * 8], ok ? W + (size_t)(n0 + r) * g.K + k0 + ch * 8 : W, ok);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  float acc[2][NT][4] = {};
+  const int steps = (g.K + BK - 1) / BK;
+  load(0, 0);
+  for (int s = 0; s < steps; ++s) {
+    if (s + 1 < steps) {
+      load((s + 1) & 1, (s + 1) * BK);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const int st = s & 1;
+    const int gq = lane >> 2, tq = lane & 3;
+#pragma unroll
+    for (int kk = 0; kk < BK; kk += 16) {
+      uint32_t af[2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        const int r = wm * 32 + mt * 16 + gq;
+        af[mt][0] = *reinterpret_cast<const uint32_t*>(&As[st][r][kk + 2 * tq]);
+        af[mt][1] = *reinterpret_cast<const uint32_t*>(&As[st][r + 8][kk + 2 * tq]);
+        af[mt][2] = *reinterpret_cast<const uint32_t*>(&As[st][r][kk + 2 * tq + 8]);
+        af[mt][3] = *reinterpret_cast<const uint32_t*>(&As[st][r + 8][kk + 2 * tq + 8]);
+      }
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int c = wn * WN + nt * 8 + gq;
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&Bs[st][c][kk + 2 * tq]);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&Bs[st][c][kk + 2 * tq + 8]);
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+          asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                       : "+f"(acc[mt][nt][0]), "+f"(acc[mt][nt][1]), "+f"(acc[mt][nt][2]), "+f"(acc[mt][nt][3])
+                       : "r"(af[mt][0]), "r"(af[mt][1]), "r"(af[mt][2]), "r"(af[mt][3]), "r"(b0), "r"(b1));
+      }
+    }
+    __syncthreads();
+  }
+  __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(g.c);
+  const int gq = lane >> 2, tq = lane & 3;
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = wm * 32 + mt * 16 + gq + half * 8;
+      if (r >= m_rows) continue;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int c = n0 + wn * WN + nt * 8 + 2 * tq;
+        __nv_bfloat16* dst = C + (size_t)(slot0 + r) * g.c_stride + c;
+        const float v0 = apply_act(acc[mt][nt][half * 2], g.act), v1 = apply_act(acc[mt][nt][half * 2 + 1], g.act);
+        if (c < g.n_out) dst[0] = __float2bfloat16_rn(v0);
+        if (c + 1 < g.n_out) dst[1] = __float2bfloat16_rn(v1);
+      }
+    }
+}
+
+// out[n, :] = sum_j weights[n, j] * y[inv[n * top + j], :] + shared[n, :]
+template <typename T>
+__global__ void expert_combine_kernel(const T* __restrict__ y, long y_stride, const int32_t* __restrict__ inv,
+                                      const float* __restrict__ weights, int top, const T* __restrict__ shared,
+                                      long shared_stride, T* __restrict__ out, long out_stride, int cols) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int n = blockIdx.x;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < top; ++j) {
+      const int slot = inv[(size_t)n * top + j];
+      if (slot >= 0) acc = __fmaf_rn(weights[(size_t)n * top + j], to_f32<T>(y[(size_t)slot * y_stride + c]), acc);
+    }
+    if (shared) acc += to_f32<T>(shared[(size_t)n * shared_stride + c]);
+    out[(size_t)n * out_stride + c] = from_f32<T>(acc);
+  }
+}
+
+}  // namespace
+
+YALIS_API int yalis_route_topk(const float* logits, int n_tokens, int E, int top, float eps, const int32_t* req_of_token,
+                               int32_t* ids, float* weights, cudaStream_t stream) {
+  if (n_tokens <= 0) return YALIS_OK;
+  if (E <= 0 || E > kMaxExperts || top <= 0 || top > kMaxTop || top > E) return YALIS_ERR_SHAPE;
+  const int warps = 4;
+  return yalis_launch(route_topk_kernel, dim3((n_tokens + warps - 1) / warps), dim3(32 * warps), 0, stream, logits, E, top,
+                      eps, req_of_token, ids, weights, n_tokens);
+}
+
+YALIS_API int yalis_expert_plan(const int32_t* ids, int entries, int E, int bm, int32_t* offsets, int32_t* perm,
+                                int32_t* inv, int32_t* tile_expert, int32_t* tile_slot, int32_t* n_tiles,
+                                cudaStream_t stream) {
+  if (entries <= 0) return YALIS_OK;
+  if (E <= 0 || E > kMaxExperts || bm <= 0) return YALIS_ERR_SHAPE;
+  return yalis_launch(expert_plan_kernel, dim3(1), dim3(1024), 0, stream, ids, entries, E, bm, offsets, perm, inv,
+                      tile_expert, tile_slot, n_tiles);
+}
+
+// bm: the row tile the plan was made for (32 or 128 for the tensor-core form, 32 for the other).
+YALIS_API int yalis_grouped_gemm(const void* a, long a_stride, const int32_t* perm, int top, const void* w, void* c,
+                                 long c_stride, int dtype, const int32_t* offsets, const int32_t* tile_expert,
+                                 const int32_t* tile_slot, const int32_t* n_tiles, int max_tiles, int n_out, int K, int act,
+                                 int bm, int tensor_cores, cudaStream_t stream) {
+  if (max_tiles <= 0) return YALIS_OK;
+  if (n_out <= 0 || K <= 0 || top <= 0 || (n_out + 63) / 64 > 65535) return YALIS_ERR_SHAPE;
+  GroupedArgs g;
+  g.a = a; g.a_stride = a_stride; g.perm = perm; g.top = top; g.w = w; g.c = c; g.c_stride = c_stride; g.offsets = offsets;
+  g.tile_expert = tile_expert; g.tile_slot = tile_slot; g.n_tiles = n_tiles; g.n_out = n_out; g.K = K; g.act = act;
+  const dim3 grid(max_tiles, (n_out + 63) / 64);
+  if (tensor_cores) {
+    if (dtype != YALIS_BF16) return YALIS_ERR_DTYPE;
+    if (K % 8 || a_stride % 8 || ((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return YALIS_ERR_ALIGN;
+    if (bm == 32) return yalis_launch(grouped_gemm_mma_kernel<32>, grid, dim3(128), 0, stream, g);
+    if (bm == 128) return yalis_launch(grouped_gemm_mma_kernel<128>, grid, dim3(128), 0, stream, g);
+    return YALIS_ERR_SHAPE;
+  }
+  if (bm != 32) return YALIS_ERR_SHAPE;
+  YALIS_DISPATCH_DTYPE(dtype, T, return yalis_launch(grouped_gemm_simt_kernel<T>, grid, dim3(256), 0, stream, g));
+  return YALIS_OK;
+}
+
+YALIS_API int yalis_expert_combine(const void* y, long y_stride, const int32_t* inv, const float* weights, int top,
+                                   const void* shared, long shared_stride, void* out, long out_stride, int dtype,
+                                   int n_tokens, int cols, cudaStream_t stream) {
+  if (n_tokens <= 0 || cols <= 0) return YALIS_OK;
+  if (top <= 0) return YALIS_ERR_SHAPE;
+  YALIS_DISPATCH_DTYPE(dtype, T,
+                       return yalis_launch(expert_combine_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (const T*)y,
+                                           y_stride, inv, weights, top, (const T*)shared, shared_stride, (T*)out,
+                                           out_stride, cols));
+  return YALIS_OK;
+}

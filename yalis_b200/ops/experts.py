@@ -1,0 +1,115 @@
+"""Wrappers of csrc/experts.cu: the kernels of a routed feed-forward (router, grouping by expert, one product
+over all experts, weighted sum).  Nothing here reads the routing on the host."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from ._lib import check, dtype_code, f32, i32, i64, lib, need, need_cuda, ptr, stream
+
+MAX_EXPERTS, MAX_TOP = 1024, 32
+ACT_NONE, ACT_RELU2 = 0, 1
+
+
+def route_topk(logits: torch.Tensor, top: int, eps: float = 1e-20, req_of_token: Optional[torch.Tensor] = None):
+    """(ids int32 [N, top], weights float32 [N, top]): the ``top`` largest of softmax(logits) per row (ties to the
+    smaller index) and those scores divided by their sum + eps.  Rows of no request get ids -1."""
+    name = "route_topk"
+    need_cuda(name, logits, req_of_token)
+    need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous(), name, "logits must be contiguous float32 [N, E]")
+    n, e = logits.shape
+    need(0 < top <= min(e, MAX_TOP) and e <= MAX_EXPERTS, name, f"needs top <= min(E, {MAX_TOP}) and E <= {MAX_EXPERTS}")
+    ids = torch.empty((n, top), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((n, top), dtype=torch.float32, device=logits.device)
+    check(lib().yalis_route_topk(ptr(logits), i32(n), i32(e), i32(top), f32(eps), ptr(req_of_token), ptr(ids), ptr(weights),
+                                 stream()), name)
+    return ids, weights
+
+
+@dataclass
+class ExpertPlan:
+    """The entries (token, choice) of a step sorted by expert: ``offsets`` [E + 1], ``perm`` slot -> entry, ``inv``
+    entry -> slot (-1: none), and the row tiles (expert, first slot) of ``bm`` slots, ``n_tiles`` of them (at most
+    ``max_tiles``, which only the shapes give)."""
+
+    offsets: torch.Tensor
+    perm: torch.Tensor
+    inv: torch.Tensor
+    tile_expert: torch.Tensor
+    tile_slot: torch.Tensor
+    n_tiles: torch.Tensor
+    max_tiles: int
+    bm: int
+    entries: int
+
+
+def expert_plan(ids: torch.Tensor, n_experts: int, bm: int) -> ExpertPlan:
+    name = "expert_plan"
+    need_cuda(name, ids)
+    need(ids.dtype == torch.int32 and ids.dim() == 2 and ids.is_contiguous(), name, "ids must be contiguous int32 [N, top]")
+    entries = ids.numel()
+    max_tiles = entries // bm + min(n_experts, entries)
+    buf = torch.empty(n_experts + 1 + 2 * entries + 2 * max_tiles + 1, dtype=torch.int32, device=ids.device)
+    o = 0
+
+    def take(count):
+        nonlocal o
+        view = buf[o:o + count]
+        o += count
+        return view
+
+    plan = ExpertPlan(take(n_experts + 1), take(entries), take(entries), take(max_tiles), take(max_tiles), take(1),
+                      max_tiles, bm, entries)
+    check(lib().yalis_expert_plan(ptr(ids), i32(entries), i32(n_experts), i32(bm), ptr(plan.offsets), ptr(plan.perm),
+                                  ptr(plan.inv), ptr(plan.tile_expert), ptr(plan.tile_slot), ptr(plan.n_tiles), stream()), name)
+    return plan
+
+
+def tensor_core_form(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the product takes the mma form: bfloat16, K a multiple of 8, rows on 16-byte boundaries."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def grouped_gemm(a: torch.Tensor, w: torch.Tensor, plan: ExpertPlan, *, gather_top: Optional[int] = None,
+                 act: int = ACT_NONE, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """C[s, :] = act(A[row(s), :] . w[expert(s)]^T) for every slot s of the plan; row(s) = perm[s] // gather_top
+    when ``gather_top`` is given (A holds one row per token), else s (A holds one row per slot).  ``w`` [E, n_out, K]."""
+    name = "grouped_gemm"
+    need_cuda(name, a, w, out)
+    need(a.dim() == 2 and w.dim() == 3 and w.is_contiguous() and a.stride(1) == 1 and a.shape[1] == w.shape[2]
+         and a.dtype == w.dtype, name, "A [rows, K], w [E, n_out, K] contiguous, one dtype")
+    n_out, k = w.shape[1], w.shape[2]
+    if out is None:
+        out = torch.empty((plan.entries, n_out), dtype=a.dtype, device=a.device)
+    need(out.shape == (plan.entries, n_out) and out.dtype == a.dtype and out.stride(1) == 1, name, "bad out tensor")
+    tc = tensor_core_form(a, w) and plan.bm in (32, 128)
+    need(tc or plan.bm == 32, name, "the plan's row tile does not fit the kernel that takes these operands")
+    check(lib().yalis_grouped_gemm(ptr(a), i64(a.stride(0)), ptr(plan.perm if gather_top else None), i32(gather_top or 1),
+                                   ptr(w), ptr(out), i64(out.stride(0)), i32(dtype_code(a.dtype)), ptr(plan.offsets),
+                                   ptr(plan.tile_expert), ptr(plan.tile_slot), ptr(plan.n_tiles), i32(plan.max_tiles),
+                                   i32(n_out), i32(k), i32(act), i32(plan.bm), i32(1 if tc else 0), stream()), name)
+    return out
+
+
+def expert_combine(y: torch.Tensor, plan: ExpertPlan, weights: torch.Tensor, shared: Optional[torch.Tensor] = None,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[n, :] = sum_j weights[n, j] * y[inv[n, j], :] (+ shared[n, :]), float32 sums in the order of j."""
+    name = "expert_combine"
+    need_cuda(name, y, weights, shared, out)
+    n, top = weights.shape
+    need(weights.dtype == torch.float32 and weights.is_contiguous() and n * top == plan.entries, name, "weights: float32 [N, top]")
+    need(y.dim() == 2 and y.shape[0] == plan.entries and y.stride(1) == 1, name, "y must be [N * top, C]")
+    cols = y.shape[1]
+    if shared is not None:
+        need(shared.shape == (n, cols) and shared.dtype == y.dtype and shared.stride(1) == 1, name, "shared must be [N, C] like y")
+    if out is None:
+        out = torch.empty((n, cols), dtype=y.dtype, device=y.device)
+    need(out.shape == (n, cols) and out.dtype == y.dtype and out.stride(1) == 1, name, "bad out tensor")
+    check(lib().yalis_expert_combine(ptr(y), i64(y.stride(0)), ptr(plan.inv), ptr(weights), i32(top), ptr(shared),
+                                     i64(shared.stride(0) if shared is not None else 0), ptr(out), i64(out.stride(0)),
+                                     i32(dtype_code(y.dtype)), i32(n), i32(cols), stream()), name)
+    return out

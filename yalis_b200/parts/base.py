@@ -400,4 +400,4 @@ def registered(category: str) -> Tuple[str, ...]:
 
 
 def _ensure_builtin() -> None:
-    from yalis_b200.parts import attention, block, dense, norm, recurrent, rotary, swiglu  # noqa: F401
+    from yalis_b200.parts import attention, block, dense, experts, latent, norm, recurrent, rotary, swiglu  # noqa: F401

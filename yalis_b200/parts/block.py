@@ -13,16 +13,24 @@ from .base import Block, Projected, ResidualStream, register_part, stack_rows
 class PreNormResidualBlock(Block):
     """x += mixer(norm_1(x)); x += feed_forward(norm_2(x))
     (the non-parallel branch of yalis/external/model.py:414-438).
-    Each addition is parked in the stream and performed by the next norm."""
+    Each addition is parked in the stream and performed by the next norm.  A layer may leave out the position part
+    (a mixer that sees to positions itself) and the feed-forward with its norm."""
 
     slots = {"position": "position", "norm_1": "norm", "mixer": "mixer", "norm_2": "norm",
              "feed_forward": "feed_forward"}
+    optional = ("position", "norm_2", "feed_forward")
+
+    def __init__(self, spec, parts):
+        super().__init__(spec, parts)
+        if ("norm_2" in self.parts) != ("feed_forward" in self.parts):
+            raise ValueError("a pre-norm block has a feed-forward and its norm, or neither")
 
     def forward(self, stream: ResidualStream, ctx, cache) -> None:
         h = self.norm_1.forward(stream)
         stream.add(self.mixer.forward(h, ctx, cache))
-        h = self.norm_2.forward(stream)
-        stream.add(self.feed_forward.forward(h, ctx))
+        if "feed_forward" in self.parts:
+            h = self.norm_2.forward(stream)
+            stream.add(self.feed_forward.forward(h, ctx))
 
 
 class ParallelResidualBlock(Block):

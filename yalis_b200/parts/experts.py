@@ -1,0 +1,91 @@
+"""A routed feed-forward: every token runs ``top`` of ``experts`` small feed-forwards, chosen and weighted by a
+router, and optionally a shared one that every token runs.
+
+    s = softmax(W_r x) over all experts (float32);  chosen = the ``top`` largest s;  w_j = s_j / (sum chosen s + eps)
+    y = sum_j w_j  D_j act(U_j x)  +  D_s act(U_s x)
+
+The router's matrix is held in float32 and its product runs on the exact kernel.  The experts' products are one
+launch each way over all experts (tokens sorted by expert on the device, nothing read back), so a step with
+routed layers launches the same kernels whatever the routing and can be recorded.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from yalis_b200.config.spec import PartSpec
+from yalis_b200.ops import experts as ops
+from yalis_b200.ops.elementwise import ACTIVATIONS, activation
+from yalis_b200.ops.linear import linear
+from .base import FeedForward, ParamSpec, register_part
+
+_GROUPED_ACT = {"relu2": ops.ACT_RELU2, "none": ops.ACT_NONE}
+
+
+class RoutedExperts(FeedForward):
+    """Parameters: ``hidden_size``, ``experts``, ``top``, ``expert_size`` (inner size of an expert), ``activation``
+    (``relu2``: the square of relu), ``shared_size`` (inner size of the shared expert; None: none), ``renorm_eps``
+    (added to the sum of the chosen scores; default 1e-20)."""
+
+    def __init__(self, spec: PartSpec):
+        super().__init__(spec)
+        p = spec.params
+        self.hidden, self.n_experts, self.top = int(p["hidden_size"]), int(p["experts"]), int(p["top"])
+        self.inner = int(p["expert_size"])
+        self.act = str(p.get("activation", "relu2"))
+        self.shared = int(p["shared_size"]) if p.get("shared_size") is not None else None
+        self.eps = float(p.get("renorm_eps", 1e-20))
+        if self.act not in _GROUPED_ACT or self.act not in ACTIVATIONS:
+            raise ValueError(f"activation {self.act!r} is not one the routed feed-forward has ({', '.join(_GROUPED_ACT)})")
+        if not 0 < self.top <= min(self.n_experts, ops.MAX_TOP) or self.n_experts > ops.MAX_EXPERTS:
+            raise ValueError(f"top {self.top} of {self.n_experts} experts is not supported "
+                             f"(top <= {ops.MAX_TOP}, experts <= {ops.MAX_EXPERTS})")
+        self.router: Optional[torch.Tensor] = None
+        self.w_up = self.w_down = self.s_up = self.s_down = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        specs = {"router": ParamSpec((self.n_experts, self.hidden), keep_float32=True)}
+        for i in range(self.n_experts):
+            specs[f"expert_{i}_up"] = ParamSpec((self.inner, self.hidden))
+            specs[f"expert_{i}_down"] = ParamSpec((self.hidden, self.inner))
+        if self.shared is not None:
+            specs["shared_up"] = ParamSpec((self.shared, self.hidden))
+            specs["shared_down"] = ParamSpec((self.hidden, self.shared))
+        return specs
+
+    def load(self, t: Dict[str, torch.Tensor]) -> None:
+        self.router = t["router"].float().contiguous()
+        self.w_up = torch.stack([t[f"expert_{i}_up"] for i in range(self.n_experts)]).contiguous()
+        self.w_down = torch.stack([t[f"expert_{i}_down"] for i in range(self.n_experts)]).contiguous()
+        if self.shared is not None:
+            self.s_up, self.s_down = t["shared_up"].contiguous(), t["shared_down"].contiguous()
+
+    def capture_key(self, host):
+        return None
+
+    def matrix_flops_per_token(self) -> float:
+        # the products a token runs: the router, ``top`` experts and the shared one
+        return 2.0 * self.hidden * (self.n_experts + 2 * self.top * self.inner + 2 * (self.shared or 0))
+
+    def row_tile(self, x: torch.Tensor) -> int:
+        """Rows of a tile of the experts' products: 128 where the tensor-core form runs and an expert gets that many
+        tokens on average, else 32."""
+        tc = (x.dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.inner % 8 == 0 and x.stride(0) % 8 == 0
+              and x.data_ptr() % 16 == 0)
+        return 128 if tc and x.shape[0] * self.top >= 96 * self.n_experts else 32
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        logits = linear(x, self.router, out_dtype=torch.float32)
+        ids, weights = ops.route_topk(logits, self.top, self.eps, ctx.req_of_token if ctx is not None else None)
+        plan = ops.expert_plan(ids, self.n_experts, self.row_tile(x))
+        inner = ops.grouped_gemm(x, self.w_up, plan, gather_top=self.top, act=_GROUPED_ACT[self.act])
+        y = ops.grouped_gemm(inner, self.w_down, plan)
+        shared = None
+        if self.shared is not None:
+            shared = linear(activation(linear(x, self.s_up), self.act), self.s_down)
+        return ops.expert_combine(y, plan, weights, shared)
+
+
+register_part("feed_forward", "routed_experts", RoutedExperts)

@@ -1,0 +1,129 @@
+"""Attention over a latent: keys and values of all heads are linear maps of one small normed vector per token.
+
+    q_h = [plain (d) | rotated (p)] of W_q x;   W_dkv x = [c~ (r) | k~ (p)]
+    c = c~ / sqrt(mean(c~^2) + eps) * n;        k_rot = rotation of k~ (one for all heads)
+    key_h(j) = [U_k,h c(j) | k_rot(j)],  value_h(j) = U_v,h c(j)
+    o_h(i) = sum_j softmax_j(q_h(i) . key_h(j) * scale) value_h(j)  over the j a window lets i see
+    y = W_o (o * sigmoid(W_g x))                (the gate is optional)
+
+Only the row [c | k_rot] of a token is cached (one "key head" of width r + p without values).  Keys and values
+are never expanded: U_k,h^T is applied to the plain part of the query and U_v,h to the weighted sum of the
+latents, which turns every head into a query over the same rows (see csrc/latent_attention.cu).  A layer may read
+the rows another layer wrote (``own_latent`` False; the schedule entry names the other with ``cache_of``).
+"""
+
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from yalis_b200.config.spec import PartSpec
+from yalis_b200.ops import latent as ops
+from .base import Mixer, PagedKV, PagedKVCache, ParamSpec, PositionEncoding, Projected, make_part, register_part, stack_rows
+
+
+class LatentAttention(Mixer, Projected):
+    """Parameters: ``hidden_size``, ``num_heads``, ``head_dim`` (d, the plain part of a query and key),
+    ``rot_dim`` (p, the rotated part), ``v_head_dim`` (e), ``kv_rank`` (r), ``rotary`` (the parameters of a
+    ``rotary`` position part whose ``head_dim`` is the number of sizes that turn, at most p; None: no rotation),
+    ``scale``, ``window`` (None: all keys), ``cache_window`` (how long rows are kept: at least ``window`` and the
+    windows of the layers that read them; None: for ever), ``norm_eps``, ``gate`` (bool), ``own_latent`` (bool)."""
+
+    def __init__(self, spec: PartSpec, position: Optional[PositionEncoding] = None):
+        p = spec.params
+        if position is None and p.get("rotary") is not None:
+            position = make_part("position", PartSpec("rotary", dict(p["rotary"])))
+        super().__init__(spec, position)
+        self.hidden, self.nh = int(p["hidden_size"]), int(p["num_heads"])
+        self.d, self.p, self.e, self.r = int(p["head_dim"]), int(p["rot_dim"]), int(p["v_head_dim"]), int(p["kv_rank"])
+        self.scale = float(p["scale"])
+        self.window = p.get("window")
+        self.cache_window = p.get("cache_window", self.window)
+        self.eps = float(p["norm_eps"])
+        self.gate = bool(p.get("gate", False))
+        self.own = bool(p.get("own_latent", True))
+        if self.r + self.p > ops.MAX_ROW:
+            raise ValueError(f"kv_rank + rot_dim = {self.r + self.p} is more than the kernels take ({ops.MAX_ROW})")
+        if self.position is not None and self.position.head_dim > self.p:
+            raise ValueError(f"{self.position.head_dim} sizes are to turn, but the rotated part has {self.p}")
+        if self.window is not None and self.cache_window is not None and self.cache_window < self.window:
+            raise ValueError("cache_window must not be smaller than window")
+        self.hidden_width = self.nh * self.e
+        self.w_in: Optional[torch.Tensor] = None
+        self.w_out: Optional[torch.Tensor] = None
+        self.uk_t = self.uv = self.norm_w = None
+        self.q_off = self.kv_off = self.g_off = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        specs = {"q_proj": ParamSpec((self.nh * (self.d + self.p), self.hidden)),
+                 "uk_proj": ParamSpec((self.nh * self.d, self.r)), "uv_proj": ParamSpec((self.nh * self.e, self.r)),
+                 "o_proj": ParamSpec((self.hidden, self.nh * self.e))}
+        if self.own:
+            specs["dkv_proj"] = ParamSpec((self.r + self.p, self.hidden))
+            specs["dkv_norm"] = ParamSpec((self.r,), init="ones", keep_float32=True)
+        if self.gate:
+            specs["g_proj"] = ParamSpec((self.nh * self.e, self.hidden))
+        return specs
+
+    def load(self, t: Dict[str, torch.Tensor]) -> None:
+        blocks, names = [t["q_proj"]], ["q"]
+        if self.own:
+            blocks.append(t["dkv_proj"])
+            names.append("kv")
+            self.norm_w = t["dkv_norm"].contiguous()
+        if self.gate:
+            blocks.append(t["g_proj"])
+            names.append("g")
+        self.w_in, spans = stack_rows(blocks)
+        at = {n: s[0] for n, s in zip(names, spans)}
+        self.q_off, self.kv_off, self.g_off = at["q"], at.get("kv"), at.get("g")
+        self.w_out = t["o_proj"].contiguous()
+        # U_k,h^T as [H, r, d] (it maps a query's plain part to the latent's size); U_v,h as stored, [H, e, r]
+        self.uk_t = t["uk_proj"].reshape(self.nh, self.d, self.r).transpose(1, 2).contiguous()
+        self.uv = t["uv_proj"].reshape(self.nh, self.e, self.r).contiguous()
+
+    def in_weight(self) -> torch.Tensor:
+        return self.w_in
+
+    def out_weight(self) -> torch.Tensor:
+        return self.w_out
+
+    def release_projections(self) -> None:
+        self.w_in = self.w_out = None
+
+    def cache_request(self) -> PagedKV:
+        return PagedKV(1, self.r + self.p, self.cache_window, v_head_dim=0)
+
+    def capture_key(self, host):
+        return ("latent_attention",)
+
+    def matrix_flops_per_token(self) -> float:
+        return super().matrix_flops_per_token()
+
+    def mixing_flops(self, q_len: int, ctx_before: int) -> float:
+        keys = sum(min(ctx_before + t + 1, self.window or (ctx_before + t + 1)) for t in range(q_len)) if self.window \
+            else q_len * ctx_before + q_len * (q_len + 1) / 2
+        return 2.0 * self.nh * (2 * self.r + self.p) * keys
+
+    def mix(self, z: torch.Tensor, ctx, cache: PagedKVCache, y: torch.Tensor) -> None:
+        n, nh, d, p, e, r = z.shape[0], self.nh, self.d, self.p, self.e, self.r
+        pos = self.position
+        freq = pos.frequencies(pos.head_dim, z.device) if pos is not None else None
+        table = ctx.block_tables[cache.group]
+        qc = torch.empty((n, nh, r + p), dtype=torch.float32, device=z.device)
+        ops.latent_prepare(z, self.q_off, self.kv_off if (self.own and cache.writable) else None, nh, d, r, p, self.norm_w,
+                           self.eps, freq, bool(pos.interleaved) if pos is not None else False,
+                           float(pos.magnitude) if pos is not None else 1.0, qc, cache.k, table, ctx.positions,
+                           ctx.req_of_token, bad_flag=ctx.error_flag)
+        q = z[:, self.q_off:self.q_off + nh * (d + p)].unflatten(1, (nh, d + p))
+        ops.head_project(q[:, :, :d], self.uk_t, qc[:, :, :r], req_of_token=ctx.req_of_token)
+        mixed = ops.latent_attention_exact(qc, cache.k, ctx.positions, ctx.req_of_token, table, r, self.scale, self.window)
+        gate = z[:, self.g_off:self.g_off + nh * e] if self.gate else None
+        ops.head_project(mixed, self.uv, y.unflatten(1, (nh, e)), gate=gate, req_of_token=ctx.req_of_token)
+
+    def forward(self, x: torch.Tensor, ctx, cache: PagedKVCache) -> torch.Tensor:
+        return self.project_and_mix(x, ctx, cache)
+
+
+register_part("mixer", "latent_attention", LatentAttention)
