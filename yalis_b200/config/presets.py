@@ -143,6 +143,83 @@ PRESETS["tirezen-1b"] = _tirezen_stack(2048, 32000, 5, 16, 128, 8, 8192)
 PRESETS["tirezen-3b"] = _tirezen_stack(3072, 32000, 8, 24, 128, 8, 8192)
 
 
+# ---- Vepivik: windowed attention and attention over a cached latent, routed feed-forwards ----------------------
+
+def _moe(experts, top, ff, shared):
+    mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+    if shared is not None:
+        mlp["shared"] = {"ff": shared}
+    return mlp
+
+
+def _windowed(heads, kv_heads, dim, vdim, window, scale, mlp):
+    return {"type": "attention", "mlp": mlp,
+            "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "mask": {"size": window}, "scale": scale}}
+
+
+def _latent(heads, dim, rot_dim, vdim, kv_rank, window, scale, rot, mlp, kv_from=None):
+    """``rot`` = (dims, base) or (dims, base, factor, original, fast, slow)."""
+    r = {"dims": rot[0], "base": rot[1]}
+    if len(rot) > 2:
+        r["scaling"] = dict(zip(("factor", "original", "fast", "slow"), rot[2:]))
+    mixer = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "mask": {"size": window},
+             "scale": scale, "rot": r}
+    if kv_from is not None:
+        mixer["kv_from"] = kv_from
+    return {"type": "latent_attention", "mixer": mixer, "mlp": mlp}
+
+
+def _vepivik(width, vocab, layers, embedding_scale=1.0, eps=1e-5) -> Dict[str, Any]:
+    return {"architecture": "Vepivik", "width": width, "vocab": vocab, "norm": {"eps": eps},
+            "embedding": {"scale": embedding_scale}, "layers": layers}
+
+
+def _vepivik_stack(width, vocab, groups, heads, kv_heads, dim, kv_rank, rot_dim, window, experts, top, ff, shared) -> Dict[str, Any]:
+    """``groups`` times (attention, latent, latent reading the one before, attention) at the sizes of a real model."""
+    rot = (rot_dim, 10000.0, 8.0, 4096, 32.0, 1.0)
+    layers = []
+    for _ in range(groups):
+        at = len(layers)
+        mlp = _moe(experts, top, ff, shared)
+        layers.append(_windowed(heads, kv_heads, dim, dim, window, dim ** -0.5, mlp))
+        layers.append(_latent(heads, dim, rot_dim, dim, kv_rank, 2 * window, (dim + rot_dim) ** -0.5, rot, mlp))
+        layers.append(_latent(heads, dim, rot_dim, dim, kv_rank, 2 * window, (dim + rot_dim) ** -0.5, rot, mlp, kv_from=at + 1))
+        layers.append(_windowed(heads, kv_heads, dim, dim, window, dim ** -0.5, mlp))
+    return _vepivik(width, vocab, layers, embedding_scale=width ** 0.5)
+
+
+_Y1 = (8, 100.0, 4.0, 32, 8.0, 2.0)
+# Test shapes.  A: a reader with a wider window than the layer whose rows it reads, a rotation of fewer sizes than the
+# rotated part has, a layer without feed-forward, one without a shared expert, a single choice.  B: sizes that are
+# multiples of nothing (no row on a 16-byte boundary), one key head, one latent head, three of five experts.
+# C: the head sizes of the tensor-core kernels, windows of one position and of a page, sixteen experts.
+# D: every expert chosen, windows that never bind, as many key heads as heads, no embedding scale.
+PRESETS["vepivik-tiny-A"] = _vepivik(64, 96, [
+    _latent(2, 8, 8, 12, 24, 20, 0.3, _Y1, _moe(4, 2, 24, 40)),
+    _windowed(4, 2, 12, 20, 9, 0.25, _moe(6, 1, 16, 16)),
+    _latent(3, 12, 8, 8, 24, 33, 0.2, _Y1, None, kv_from=0),
+    _windowed(2, 2, 16, 16, 16, 0.35, _moe(4, 3, 32, None)),
+    _latent(2, 10, 6, 14, 16, 11, 0.28, (4, 50.0), _moe(4, 2, 24, 8))], embedding_scale=2.5)
+PRESETS["vepivik-tiny-B"] = _vepivik(36, 50, [
+    _windowed(3, 1, 10, 6, 5, 0.3, _moe(5, 3, 18, None)),
+    _latent(1, 6, 4, 10, 14, 7, 0.4, (4, 20.0, 3.0, 16, 4.0, 0.5), _moe(3, 2, 10, 14)),
+    _latent(3, 5, 4, 7, 14, 3, 0.35, (4, 20.0, 3.0, 16, 4.0, 0.5), _moe(5, 3, 18, 6), kv_from=1)],
+    embedding_scale=0.7, eps=1e-6)
+PRESETS["vepivik-tiny-C"] = _vepivik(128, 160, [
+    _latent(4, 32, 32, 32, 64, 64, 0.12, (32, 10000.0, 2.0, 64, 16.0, 1.0), _moe(16, 4, 32, 64)),
+    _windowed(4, 2, 64, 64, 1, 0.125, _moe(16, 4, 32, 64)),
+    _windowed(2, 1, 64, 64, 64, 0.125, _moe(8, 2, 64, None)),
+    _latent(8, 16, 32, 16, 64, 17, 0.15, (32, 10000.0, 2.0, 64, 16.0, 1.0), _moe(16, 4, 32, 64), kv_from=0)],
+    embedding_scale=3.0)
+PRESETS["vepivik-tiny-D"] = _vepivik(48, 64, [
+    _windowed(2, 2, 8, 24, 4096, 0.3, _moe(2, 2, 20, 12)),
+    _latent(2, 16, 2, 8, 20, 4096, 0.25, (2, 7.0), _moe(2, 2, 20, 12))], embedding_scale=1.0)
+# Sizes that resemble a real model's layers (random weights, for the benchmark): about a billion weights of which
+# a token uses a quarter; head size 128 so that the windowed attention runs on the tensor cores.
+PRESETS["vepivik-1b"] = _vepivik_stack(2048, 32000, 4, 16, 8, 128, 256, 64, 1024, 16, 2, 2048, 2048)
+PRESETS["vepivik-3b"] = _vepivik_stack(3072, 32000, 6, 24, 8, 128, 384, 64, 1024, 32, 4, 1536, 3072)
+
+
 def preset(name: str) -> Dict[str, Any]:
     """A fresh copy of the named configuration dictionary."""
     for key in (name, name.split("/")[-1], name.split("/")[-1].replace("Meta-", "")):
