@@ -444,8 +444,14 @@ def test_other_block_arrangements_and_model_hooks(dtype):
     from yalis_b200.parts.base import build_block
     spec = ToyArchitecture.model_spec(c)
     assert sorted(build_block(spec.layers[1]).parts) == ["mixer", "norm_1", "position"]
-    with pytest.raises(ValueError, match="feed_forward"):
-        build_block(LayerSpec(PartSpec("pre_norm_residual"), spec.layers[1].parts, "x.", {}))       # a place left empty
+    without_norm = {k: v for k, v in spec.layers[1].parts.items() if k != "norm_1"}
+    with pytest.raises(ValueError, match="norm_1"):
+        build_block(LayerSpec(PartSpec("pre_norm_residual"), without_norm, "x.", {}))               # a place left empty
+    assert sorted(build_block(LayerSpec(PartSpec("pre_norm_residual"), spec.layers[1].parts, "x.", {})).parts) == \
+        ["mixer", "norm_1", "position"]                                                             # the feed-forward may be left out
+    lone = {k: v for k, v in spec.layers[2].parts.items() if k != "norm_2"}
+    with pytest.raises(ValueError, match="neither"):
+        build_block(LayerSpec(PartSpec("pre_norm_residual"), lone, "x.", {}))                       # but not its norm alone
     with pytest.raises(ValueError, match="after"):
         build_block(LayerSpec(PartSpec("pre_norm_residual"), spec.layers[0].parts, "x.", {}))       # a place the block lacks
 
