@@ -175,6 +175,59 @@ def test_latent_attention_sees_exactly_its_window(dtype, r, p, page, window):
                 assert hit < 0.5, (name, a, hit)
 
 
+@pytest.mark.parametrize("r, p, page, window, heads", [(64, 32, 8, 64, 3), (96, 16, 16, 37, 4), (128, 0, 64, None, 2),
+                                                      (256, 64, 16, 100, 16), (512, 64, 32, 150, 5), (384, 48, 16, 1, 8)])
+def test_latent_attention_on_the_tensor_cores(r, p, page, window, heads):
+    """The same sums by the tensor-core form: two requests in one step (a portion of 45 tokens behind 250 cached ones
+    beside a single token), the planted row at the window's edge of some of the portion's tokens; queries given in
+    float32 and, head-major, in bfloat16; results taken in both forms."""
+    from yalis_b200.ops.latent import latent_attention_mma
+    g = torch.Generator().manual_seed(r + p)
+    W = window or 10 ** 6
+    lens, new = [295, 130], [45, 1]
+    first = lens[0] - new[0]                                                      # position of the portion's first token
+    star = first + 20 - (W - 1) if window and first + 20 - (W - 1) >= 0 else 7    # seen by the portion's first 21 tokens only
+    u = torch.nn.functional.normalize(torch.randn(r + p, generator=g), dim=0)
+    rows, tables, pages_used = [], [], 0
+    pool = torch.full((sum(-(-l // page) for l in lens) + 2, 1, page, r + p), float("nan"), dtype=torch.bfloat16, device=DEV)
+    width = max(-(-l // page) for l in lens)
+    table = torch.full((2, width), -1, dtype=torch.int32)
+    perm = torch.randperm(pool.shape[0], generator=g).tolist()
+    for i, l in enumerate(lens):
+        rw = torch.randn(l, r + p, generator=g) * 0.3
+        if i == 0:
+            rw[star] = 6.0 * u
+        rw = rw.to(torch.bfloat16)
+        rows.append(rw)
+        for t in range(l):
+            if t % page == 0:
+                table[i, t // page] = perm.pop()
+            pool[int(table[i, t // page]), 0, t % page] = rw[t].to(DEV)
+    positions = list(range(first, lens[0])) + [lens[1] - 1]
+    n = len(positions)
+    qc = (torch.randn(n, heads, r + p, generator=g) * 0.3)
+    qc[:, 1] = 4.0 * u
+    qc = qc.to(torch.bfloat16).float()                                            # what both forms of the queries can hold
+    q_start, table = i32([0, new[0], n]), table.to(DEV)
+    out32 = torch.zeros(n, heads, r, device=DEV)
+    qd = qc.to(DEV)
+    latent_attention_mma(qd[:, :, :r], qd[:, :, r:], out32, pool, i32(positions), q_start, table, 2, max(new), 0.5, window)
+    q_lat = qc[:, :, :r].to(torch.bfloat16).transpose(0, 1).contiguous().to(DEV)            # [H, N, r]
+    out16 = torch.zeros(heads, n, r, dtype=torch.bfloat16, device=DEV)
+    latent_attention_mma(q_lat.transpose(0, 1), qd[:, :, r:].contiguous(), out16.transpose(0, 1), pool, i32(positions), q_start,
+                         table, 2, max(new), 0.5, window)
+    for j, a in enumerate(positions):
+        which = 0 if j < new[0] else 1
+        for h in range(heads):
+            want = plain_rows_attention(qc[j, h].double(), rows[which].double(), r, 0.5, window, a)
+            torch.testing.assert_close(out32[j, h].double().cpu(), want, rtol=3e-3, atol=3e-3, msg=lambda m: f"position {a} head {h}: {m}")
+            torch.testing.assert_close(out16[h, j].double().cpu(), want, rtol=2e-2, atol=2e-2)
+        if which == 0 and heads > 1:
+            hit = float(torch.dot(out32[j, 1].double().cpu(), rows[0][star, :r].double()) / rows[0][star, :r].double().norm() ** 2)
+            assert (hit > 0.9) == (star <= a <= star + W - 1), (a, hit)
+
+
+
 @pytest.mark.parametrize("dtype, hs, vd, page, window", [(torch.float32, 12, 20, 16, 9), (torch.bfloat16, 48, 32, 16, 40),
                                                          (torch.float32, 10, 6, 8, 5), (torch.bfloat16, 64, 64, 64, 64)])
 def test_windowed_attention_without_positions_sees_exactly_its_window(dtype, hs, vd, page, window):

@@ -9,8 +9,9 @@
 // which is attention with one key/value head of width r + p whose values are the first r sizes of the keys.
 // The pieces here: `latent_prepare` (norm of c, rotation of k_rot and of the queries' rotated parts, page
 // write), `head_project` (the per-head maps Uk^T and Uv on the CUDA cores, float32 in k order, with an optional
-// sigmoid gate on the result), and the attention itself in two forms: an exact one (float32 path, twin of the
-// other) and a tensor-core one (bfloat16 pages).  Scores, weights and sums are float32 in every form.
+// sigmoid gate on the result; large bfloat16 steps use the library's batched product and `sigmoid_gate` instead),
+// and the attention itself in two forms: an exact one (float32 path, twin of the other) and a tensor-core one
+// (bfloat16 pages).  Scores, weights and sums are float32 in every form.
 #include "common.cuh"
 
 
@@ -114,16 +115,17 @@ __global__ void head_project_kernel(const TX* __restrict__ x, long xs_n, long xs
   }
 }
 
-// y[n, c] = x[n, c] * sigmoid(g[n, c])  (x float32 or model dtype, y model dtype)
+// y[n, h * e + c] = x[n, h, c] * sigmoid(g[n, h * e + c])  (x float32 or model dtype with strides over n and h,
+// y and g model dtype)
 template <typename T, typename TX>
-__global__ void sigmoid_gate_kernel(const TX* __restrict__ x, long xs, const T* __restrict__ g, long gs,
+__global__ void sigmoid_gate_kernel(const TX* __restrict__ x, long xs_n, long xs_h, int e, const T* __restrict__ g, long gs,
                                     T* __restrict__ y, long ys, int rows, int cols) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t total = (size_t)rows * cols;
-  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
-    const size_t r = e / cols, c = e - r * cols;
-    const float v = to_f32<TX>(x[r * xs + c]) / (1.0f + expf(-to_f32<T>(g[r * gs + c])));
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / cols, c = i - r * cols, h = c / e;
+    const float v = to_f32<TX>(x[r * xs_n + h * xs_h + (c - h * e)]) / (1.0f + expf(-to_f32<T>(g[r * gs + c])));
     y[r * ys + c] = from_f32<T>(v);
   }
 }
@@ -213,6 +215,277 @@ __global__ void latent_attention_exact_kernel(const float* __restrict__ qc, floa
   }
 }
 
+// ---- the tensor-core attention ------------------------------------------------------------------------------------------
+// bfloat16 rows, mma.sync.m16n8k16 with float32 accumulators.  All heads of a token read the same rows, so a tile
+// of 32 query rows is (tokens x heads) of one request in token order: a decode step fills it with the heads of one
+// token, a prompt portion with several tokens.  A block walks the rows its tile can see 64 at a time (cp.async, two
+// buffers, a page lookup per row).  Per 64 rows: each of the 4 warps computes the scores of 16 of them for all 32
+// queries (K = r + p), the row maxima meet in shared memory, the weights exp(s - m) go to shared memory as TWO
+// bfloat16 halves (rounding and rounding of the rest: 16 bits of mantissa, since weights are 32-bit by the design's
+// rule), and each warp then adds weights x rows[:, its quarter of the r columns] to its accumulators (the rows are
+// the B operand through ldmatrix.trans).  Maxima, sums and accumulators are float32.
+constexpr int kQRows = 32, kKeyTile = 64;
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+struct LatentMma {
+  const void* q_lat; int q_lat_bf16; long ql_n, ql_h;   // [.., r] per (token, head): float32 or bfloat16, any strides
+  const float* q_rot; long qr_n, qr_h;                  // [.., p] per (token, head)
+  void* out; int out_bf16; long o_n, o_h;               // [.., r] per (token, head)
+  const __nv_bfloat16* pool;
+  const int32_t* positions; const int32_t* q_start;
+  const int32_t* block_table; int table_width, page_size, num_pages;
+  int heads, p; float scale; int window;
+};
+
+template <int R>
+__global__ void __launch_bounds__(128) latent_attention_mma_kernel(const LatentMma a) {
+  constexpr int NT = R / 32;                       // 8-column tiles of the output a warp owns
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int W = R + a.p, LD = W + 8;               // rows of (W + 8) * 2 bytes: fragment loads hit 32 distinct banks
+  constexpr int LDP = kKeyTile + 8;
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [32][LD]
+  __nv_bfloat16* Ks = Qs + kQRows * LD;                                      // [2][64][LD]
+  __nv_bfloat16* Ph = Ks + 2 * kKeyTile * LD;                                // [32][LDP]
+  __nv_bfloat16* Pl = Ph + kQRows * LDP;                                     // [32][LDP]
+  float* red = reinterpret_cast<float*>(Pl + kQRows * LDP);                  // [4][32]
+  int* row_pos = reinterpret_cast<int*>(red + 4 * kQRows);                   // [32]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int req = blockIdx.y;
+  const int q0 = a.q_start[req], q_len = a.q_start[req + 1] - q0;
+  const int n_rows = q_len * a.heads, row0 = blockIdx.x * kQRows;
+  if (row0 >= n_rows) return;
+  const int rows_here = min(kQRows, n_rows - row0);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gq = lane >> 2, tq = lane & 3;
+
+  // the tile's queries as bfloat16, and each row's position
+  for (int i = tid; i < kQRows * W; i += 128) {
+    const int r = i / W, c = i - r * W;
+    float v = 0.f;
+    if (r < rows_here) {
+      const int tok = q0 + (row0 + r) / a.heads, h = (row0 + r) % a.heads;
+      if (c < R) {
+        v = a.q_lat_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.q_lat)[(size_t)tok * a.ql_n + (size_t)h * a.ql_h + c])
+                         : reinterpret_cast<const float*>(a.q_lat)[(size_t)tok * a.ql_n + (size_t)h * a.ql_h + c];
+      } else {
+        v = a.q_rot[(size_t)tok * a.qr_n + (size_t)h * a.qr_h + (c - R)];
+      }
+    }
+    Qs[r * LD + c] = __float2bfloat16_rn(v);
+  }
+  if (tid < kQRows) row_pos[tid] = tid < rows_here ? a.positions[q0 + (row0 + tid) / a.heads] : -1;
+  const int pos_first = a.positions[q0 + row0 / a.heads];
+  const int pos_last = a.positions[q0 + (row0 + rows_here - 1) / a.heads];
+  const int lo = (a.window > 0 && pos_first - a.window + 1 > 0) ? pos_first - a.window + 1 : 0;
+  const int n_tiles = (pos_last - lo) / kKeyTile + 1;
+  const int32_t* bt = a.block_table + (size_t)req * a.table_width;
+  const int chunks = W / 8;
+
+  auto load = [&](int tile) {
+    // two threads per row: one page lookup each, then alternate 16-byte pieces
+    __nv_bfloat16* dst = Ks + (size_t)(tile & 1) * kKeyTile * LD;
+    const int r = tid >> 1, j = lo + tile * kKeyTile + r;
+    const __nv_bfloat16* src = a.pool;
+    bool ok = j <= pos_last;
+    if (ok) {
+      const int pi = j / a.page_size;
+      const int page = pi < a.table_width ? bt[pi] : -1;
+      ok = page >= 0 && page < a.num_pages;
+      if (ok) src = a.pool + ((size_t)page * a.page_size + (j - pi * a.page_size)) * W;
+    }
+    for (int ch = tid & 1; ch < chunks; ch += 2) cp_async_16(dst + r * LD + ch * 8, ok ? src + ch * 8 : a.pool, ok);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  float o[2][NT][4] = {};
+  float m_run[2][2], l_run[2][2];                  // [m-tile][row g / row g + 8]; l: this warp's share of the sum
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      m_run[mt][hf] = -INFINITY;
+      l_run[mt][hf] = 0.f;
+    }
+
+  load(0);
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();                                // tile `tile` is in place; everyone is done with tile - 1
+    if (tile + 1 < n_tiles) load(tile + 1);
+    const __nv_bfloat16* Kt = Ks + (size_t)(tile & 1) * kKeyTile * LD;
+    // scores of this warp's 16 rows for all 32 queries
+    float s[2][2][4] = {};
+    for (int k0 = 0; k0 < W; k0 += 16) {
+      uint32_t af[2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        const __nv_bfloat16* qp = Qs + (mt * 16 + gq) * LD + k0 + 2 * tq;
+        af[mt][0] = *reinterpret_cast<const uint32_t*>(qp);
+        af[mt][1] = *reinterpret_cast<const uint32_t*>(qp + 8 * LD);
+        af[mt][2] = *reinterpret_cast<const uint32_t*>(qp + 8);
+        af[mt][3] = *reinterpret_cast<const uint32_t*>(qp + 8 * LD + 8);
+      }
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        const __nv_bfloat16* kp = Kt + (warp * 16 + nt * 8 + gq) * LD + k0 + 2 * tq;
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kp), b1 = *reinterpret_cast<const uint32_t*>(kp + 8);
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) mma_bf16(s[mt][nt], af[mt], b0, b1);
+      }
+    }
+    // mask, scale, row maxima of this warp's keys
+    const int key0 = lo + tile * kKeyTile + warp * 16;
+    float mx[2][2];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const int pos = row_pos[mt * 16 + gq + hf * 8];
+        float m = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int j = key0 + nt * 8 + 2 * tq + e;
+            const bool vis = pos >= 0 && j <= pos && (a.window <= 0 || j > pos - a.window);
+            const float v = vis ? s[mt][nt][hf * 2 + e] * a.scale : -INFINITY;
+            s[mt][nt][hf * 2 + e] = v;
+            m = fmaxf(m, v);
+          }
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+        mx[mt][hf] = m;
+        if (tq == 0) red[warp * kQRows + mt * 16 + gq + hf * 8] = m;
+      }
+    __syncthreads();
+    float corr[2][2];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const int r = mt * 16 + gq + hf * 8;
+        const float m_new = fmaxf(fmaxf(m_run[mt][hf], fmaxf(red[r], red[kQRows + r])), fmaxf(red[2 * kQRows + r], red[3 * kQRows + r]));
+        corr[mt][hf] = m_new == -INFINITY ? 1.f : expf(m_run[mt][hf] - m_new);
+        m_run[mt][hf] = m_new;
+        float sum = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          float pv[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float v = s[mt][nt][hf * 2 + e];
+            pv[e] = v == -INFINITY ? 0.f : expf(v - m_new);
+            sum += pv[e];
+          }
+          const __nv_bfloat162 hi = __floats2bfloat162_rn(pv[0], pv[1]);
+          const __nv_bfloat162 lw = __floats2bfloat162_rn(pv[0] - __bfloat162float(hi.x), pv[1] - __bfloat162float(hi.y));
+          const int c = warp * 16 + nt * 8 + 2 * tq;
+          *reinterpret_cast<__nv_bfloat162*>(Ph + r * LDP + c) = hi;
+          *reinterpret_cast<__nv_bfloat162*>(Pl + r * LDP + c) = lw;
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        l_run[mt][hf] = l_run[mt][hf] * corr[mt][hf] + sum;
+      }
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        o[mt][nt][0] *= corr[mt][0];
+        o[mt][nt][1] *= corr[mt][0];
+        o[mt][nt][2] *= corr[mt][1];
+        o[mt][nt][3] *= corr[mt][1];
+      }
+    __syncthreads();                                // the weights of all 64 rows are in place
+    // this warp's quarter of the columns: o += P . rows[:, quarter]
+#pragma unroll
+    for (int kk = 0; kk < kKeyTile; kk += 16) {
+      uint32_t ah[2][4], al[2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        const int off = (mt * 16 + gq) * LDP + kk + 2 * tq;
+        ah[mt][0] = *reinterpret_cast<const uint32_t*>(Ph + off);
+        ah[mt][1] = *reinterpret_cast<const uint32_t*>(Ph + off + 8 * LDP);
+        ah[mt][2] = *reinterpret_cast<const uint32_t*>(Ph + off + 8);
+        ah[mt][3] = *reinterpret_cast<const uint32_t*>(Ph + off + 8 * LDP + 8);
+        al[mt][0] = *reinterpret_cast<const uint32_t*>(Pl + off);
+        al[mt][1] = *reinterpret_cast<const uint32_t*>(Pl + off + 8 * LDP);
+        al[mt][2] = *reinterpret_cast<const uint32_t*>(Pl + off + 8);
+        al[mt][3] = *reinterpret_cast<const uint32_t*>(Pl + off + 8 * LDP + 8);
+      }
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        // rows kk .. kk + 15 of the tile, 8 columns: lanes 0-15 name the 16 row starts
+        const __nv_bfloat16* vp = Kt + (kk + (lane & 15)) * LD + warp * (R / 4) + nt * 8;
+        uint32_t b0, b1;
+        const unsigned addr = (unsigned)__cvta_generic_to_shared(vp);
+        asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          mma_bf16(o[mt][nt], ah[mt], b0, b1);
+          mma_bf16(o[mt][nt], al[mt], b0, b1);
+        }
+      }
+    }
+  }
+  // the four warps' shares of the sums, in warp order
+  __syncthreads();
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf)
+      if (tq == 0) red[warp * kQRows + mt * 16 + gq + hf * 8] = l_run[mt][hf];
+  __syncthreads();
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int r = mt * 16 + gq + hf * 8;
+      if (r >= rows_here) continue;
+      const float l = ((red[r] + red[kQRows + r]) + red[2 * kQRows + r]) + red[3 * kQRows + r];
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      const int tok = q0 + (row0 + r) / a.heads, h = (row0 + r) % a.heads;
+      const size_t base = (size_t)tok * a.o_n + (size_t)h * a.o_h + warp * (R / 4);
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const float v0 = o[mt][nt][hf * 2] * inv, v1 = o[mt][nt][hf * 2 + 1] * inv;
+        const int c = nt * 8 + 2 * tq;
+        if (a.out_bf16) {
+          reinterpret_cast<__nv_bfloat16*>(a.out)[base + c] = __float2bfloat16_rn(v0);
+          reinterpret_cast<__nv_bfloat16*>(a.out)[base + c + 1] = __float2bfloat16_rn(v1);
+        } else {
+          reinterpret_cast<float*>(a.out)[base + c] = v0;
+          reinterpret_cast<float*>(a.out)[base + c + 1] = v1;
+        }
+      }
+    }
+}
+
+template <int R>
+int launch_latent_mma(const LatentMma& a, int max_rows, int n_requests, cudaStream_t stream) {
+  const int W = R + a.p, LD = W + 8;
+  const size_t smem = (size_t)(kQRows + 2 * kKeyTile) * LD * 2 + 2 * (size_t)kQRows * (kKeyTile + 8) * 2 + 4 * kQRows * 4 + kQRows * 4;
+  static size_t configured = 0;
+  if (smem > configured) {
+    if (cudaFuncSetAttribute(latent_attention_mma_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return YALIS_ERR_LAUNCH;
+    configured = smem;
+  }
+  const dim3 grid((max_rows + kQRows - 1) / kQRows, n_requests);
+  return yalis_launch(latent_attention_mma_kernel<R>, grid, dim3(128), smem, stream, a);
+}
+
 }  // namespace
 
 YALIS_API int yalis_latent_prepare(const void* src, int dtype, int src_stride, int q_off, int kv_off, int heads, int d,
@@ -255,20 +528,21 @@ YALIS_API int yalis_head_project(const void* x, int x_dtype, long xs_n, long xs_
   return YALIS_ERR_DTYPE;
 }
 
-YALIS_API int yalis_sigmoid_gate(const void* x, int x_dtype, long xs, const void* g, long gs, void* y, long ys, int dtype,
-                                 int rows, int cols, cudaStream_t stream) {
+YALIS_API int yalis_sigmoid_gate(const void* x, int x_dtype, long xs_n, long xs_h, int e, const void* g, long gs, void* y,
+                                 long ys, int dtype, int rows, int cols, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return YALIS_OK;
+  if (e <= 0 || cols % e) return YALIS_ERR_SHAPE;
   const size_t total = (size_t)rows * cols;
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   if (dtype == YALIS_F32 && x_dtype == YALIS_F32)
-    return yalis_launch(sigmoid_gate_kernel<float, float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, xs,
+    return yalis_launch(sigmoid_gate_kernel<float, float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, xs_n, xs_h, e,
                         (const float*)g, gs, (float*)y, ys, rows, cols);
   if (dtype == YALIS_BF16 && x_dtype == YALIS_F32)
-    return yalis_launch(sigmoid_gate_kernel<__nv_bfloat16, float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, xs,
-                        (const __nv_bfloat16*)g, gs, (__nv_bfloat16*)y, ys, rows, cols);
+    return yalis_launch(sigmoid_gate_kernel<__nv_bfloat16, float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, xs_n,
+                        xs_h, e, (const __nv_bfloat16*)g, gs, (__nv_bfloat16*)y, ys, rows, cols);
   if (dtype == YALIS_BF16 && x_dtype == YALIS_BF16)
     return yalis_launch(sigmoid_gate_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(blocks), dim3(256), 0, stream,
-                        (const __nv_bfloat16*)x, xs, (const __nv_bfloat16*)g, gs, (__nv_bfloat16*)y, ys, rows, cols);
+                        (const __nv_bfloat16*)x, xs_n, xs_h, e, (const __nv_bfloat16*)g, gs, (__nv_bfloat16*)y, ys, rows, cols);
   return YALIS_ERR_DTYPE;
 }
 
@@ -286,4 +560,37 @@ YALIS_API int yalis_latent_attention_exact(const float* qc, float* out, const vo
                                            (const T*)pool, positions, req_of_token, block_table, table_width, page_size,
                                            num_pages, heads, r, p, scale, window));
   return YALIS_OK;
+}
+
+// Whether the tensor-core form takes these sizes: r one of 64, 96, 128, 256, 384, 512 and p a multiple of 16 with
+// (32 + 128) rows of r + p + 8 bfloat16 within an SM's shared memory.
+YALIS_API int yalis_latent_attention_mma_supports(int r, int p) {
+  if (!(r == 64 || r == 96 || r == 128 || r == 256 || r == 384 || r == 512) || p < 0 || p % 16) return 0;
+  return (size_t)(kQRows + 2 * kKeyTile) * (r + p + 8) * 2 + 10240 <= 227 * 1024 ? 1 : 0;
+}
+
+// max_q_len: the longest portion of the step (bounds the grid); q_lat / out: float32 or bfloat16 by their flags.
+YALIS_API int yalis_latent_attention_mma(const void* q_lat, int q_lat_bf16, long ql_n, long ql_h, const float* q_rot, long qr_n,
+                                         long qr_h, void* out, int out_bf16, long o_n, long o_h, const void* pool,
+                                         const int32_t* positions, const int32_t* q_start, const int32_t* block_table,
+                                         int table_width, int page_size, int num_pages, int n_requests, int max_q_len,
+                                         int heads, int r, int p, float scale, int window, cudaStream_t stream) {
+  if (n_requests <= 0 || max_q_len <= 0) return YALIS_OK;
+  if (!yalis_latent_attention_mma_supports(r, p) || heads <= 0 || n_requests > 65535) return YALIS_ERR_SHAPE;
+  if ((uintptr_t)pool & 15) return YALIS_ERR_ALIGN;
+  LatentMma a;
+  a.q_lat = q_lat; a.q_lat_bf16 = q_lat_bf16; a.ql_n = ql_n; a.ql_h = ql_h; a.q_rot = q_rot; a.qr_n = qr_n; a.qr_h = qr_h;
+  a.out = out; a.out_bf16 = out_bf16; a.o_n = o_n; a.o_h = o_h; a.pool = (const __nv_bfloat16*)pool; a.positions = positions;
+  a.q_start = q_start; a.block_table = block_table; a.table_width = table_width; a.page_size = page_size;
+  a.num_pages = num_pages; a.heads = heads; a.p = p; a.scale = scale; a.window = window;
+  const int max_rows = max_q_len * heads;
+  switch (r) {
+    case 64: return launch_latent_mma<64>(a, max_rows, n_requests, stream);
+    case 96: return launch_latent_mma<96>(a, max_rows, n_requests, stream);
+    case 128: return launch_latent_mma<128>(a, max_rows, n_requests, stream);
+    case 256: return launch_latent_mma<256>(a, max_rows, n_requests, stream);
+    case 384: return launch_latent_mma<384>(a, max_rows, n_requests, stream);
+    case 512: return launch_latent_mma<512>(a, max_rows, n_requests, stream);
+  }
+  return YALIS_ERR_SHAPE;
 }

@@ -75,13 +75,15 @@ def head_project(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: Opti
 
 
 def sigmoid_gate(x: torch.Tensor, g: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
-    """y = x * sigmoid(g), [N, C] each with unit inner stride; x float32 or the dtype of g and y."""
+    """y[n, h * e + c] = x[n, h, c] * sigmoid(g[n, h * e + c]): ``x`` [N, H, e] with any strides over n and h (float32
+    or the dtype of g and y), ``g`` and ``y`` [N, H * e] with unit inner stride."""
     name = "sigmoid_gate"
     need_cuda(name, x, g, y)
-    need(x.dim() == 2 and x.shape == g.shape == y.shape and x.stride(1) == g.stride(1) == y.stride(1) == 1
-         and g.dtype == y.dtype, name, "x, g, y must be [N, C] with unit inner stride, g and y of one dtype")
-    check(lib().yalis_sigmoid_gate(ptr(x), i32(dtype_code(x.dtype)), i64(x.stride(0)), ptr(g), i64(g.stride(0)), ptr(y),
-                                   i64(y.stride(0)), i32(dtype_code(y.dtype)), i32(x.shape[0]), i32(x.shape[1]), stream()), name)
+    need(x.dim() == 3 and g.dim() == 2 and x.stride(2) == 1 and g.shape == y.shape == (x.shape[0], x.shape[1] * x.shape[2])
+         and g.stride(1) == y.stride(1) == 1 and g.dtype == y.dtype, name, "x [N, H, e]; g, y [N, H * e] of one dtype")
+    check(lib().yalis_sigmoid_gate(ptr(x), i32(dtype_code(x.dtype)), i64(x.stride(0)), i64(x.stride(1)), i32(x.shape[2]), ptr(g),
+                                   i64(g.stride(0)), ptr(y), i64(y.stride(0)), i32(dtype_code(y.dtype)), i32(g.shape[0]),
+                                   i32(g.shape[1]), stream()), name)
     return y
 
 
@@ -109,4 +111,38 @@ def latent_attention_exact(qc: torch.Tensor, pool: torch.Tensor, positions: torc
                                              ptr(req_of_token), ptr(block_table), i32(block_table.shape[1]),
                                              i32(pool.shape[2]), i32(pool.shape[0]), i32(n), i32(h), i32(r), i32(w - r),
                                              f32(scale), i32(window or 0), stream()), name)
+    return out
+
+
+def mma_supports(r: int, p: int) -> bool:
+    """Whether the tensor-core form takes a latent of ``r`` and a rotated part of ``p`` sizes."""
+    return bool(lib().yalis_latent_attention_mma_supports(i32(r), i32(p)))
+
+
+def latent_attention_mma(q_lat: torch.Tensor, q_rot: torch.Tensor, out: torch.Tensor, pool: torch.Tensor,
+                         positions: torch.Tensor, q_start: torch.Tensor, block_table: torch.Tensor, n_requests: int,
+                         max_q_len: int, scale: float, window: Optional[int]) -> torch.Tensor:
+    """The same sums as ``latent_attention_exact`` on the tensor cores, for bfloat16 rows.  ``q_lat`` [N, H, r]
+    (float32 or bfloat16) and ``q_rot`` [N, H, p] (float32) are the two parts of the queries and ``out`` [N, H, r]
+    (float32 or bfloat16) the result, each with any strides over n and h and unit inner stride.  ``q_start`` int32
+    [R + 1] gives each request's token range; ``max_q_len`` bounds the grid.  Queries and rows meet as bfloat16 with
+    float32 sums; the weights meet the rows in two bfloat16 halves."""
+    name = "latent_attention_mma"
+    need_cuda(name, q_lat, q_rot, out, pool, positions, q_start, block_table)
+    n, h, r = q_lat.shape
+    p = q_rot.shape[2]
+    need(q_rot.shape == (n, h, p) and out.shape == (n, h, r) and q_rot.dtype == torch.float32
+         and q_lat.stride(2) == q_rot.stride(2) == out.stride(2) == 1, name, "q_lat [N, H, r], q_rot float32 [N, H, p], out [N, H, r]")
+    need(q_lat.dtype in (torch.float32, torch.bfloat16) and out.dtype in (torch.float32, torch.bfloat16), name, "float32 or bfloat16")
+    need(pool.dtype == torch.bfloat16 and pool.dim() == 4 and pool.shape[1] == 1 and pool.shape[3] == r + p and pool.is_contiguous(),
+         name, "pool must be contiguous bfloat16 [pages, 1, page_size, r + p]")
+    need(mma_supports(r, p), name, f"r = {r}, p = {p} is not a shape of the tensor-core form")
+    need(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous() and q_start.dtype == torch.int32
+         and q_start.numel() >= n_requests + 1, name, "block_table int32 [R, width], q_start int32 [R + 1]")
+    check(lib().yalis_latent_attention_mma(
+        ptr(q_lat), i32(q_lat.dtype == torch.bfloat16), i64(q_lat.stride(0)), i64(q_lat.stride(1)), ptr(q_rot),
+        i64(q_rot.stride(0)), i64(q_rot.stride(1)), ptr(out), i32(out.dtype == torch.bfloat16), i64(out.stride(0)),
+        i64(out.stride(1)), ptr(pool), ptr(positions), ptr(q_start), ptr(block_table), i32(block_table.shape[1]),
+        i32(pool.shape[2]), i32(pool.shape[0]), i32(n_requests), i32(max_q_len), i32(h), i32(r), i32(p), f32(scale),
+        i32(window or 0), stream()), name)
     return out

@@ -52,7 +52,7 @@ class LatentAttention(Mixer, Projected):
         self.hidden_width = self.nh * self.e
         self.w_in: Optional[torch.Tensor] = None
         self.w_out: Optional[torch.Tensor] = None
-        self.uk_t = self.uv = self.norm_w = None
+        self.uk = self.uk_t = self.uv = self.uv_t = self.norm_w = None
         self.q_off = self.kv_off = self.g_off = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
@@ -80,8 +80,10 @@ class LatentAttention(Mixer, Projected):
         self.q_off, self.kv_off, self.g_off = at["q"], at.get("kv"), at.get("g")
         self.w_out = t["o_proj"].contiguous()
         # U_k,h^T as [H, r, d] (it maps a query's plain part to the latent's size); U_v,h as stored, [H, e, r]
-        self.uk_t = t["uk_proj"].reshape(self.nh, self.d, self.r).transpose(1, 2).contiguous()
+        self.uk = t["uk_proj"].reshape(self.nh, self.d, self.r).contiguous()
+        self.uk_t = self.uk.transpose(1, 2).contiguous()
         self.uv = t["uv_proj"].reshape(self.nh, self.e, self.r).contiguous()
+        self.uv_t = self.uv.transpose(1, 2).contiguous()
 
     def in_weight(self) -> torch.Tensor:
         return self.w_in
@@ -95,11 +97,16 @@ class LatentAttention(Mixer, Projected):
     def cache_request(self) -> PagedKV:
         return PagedKV(1, self.r + self.p, self.cache_window, v_head_dim=0)
 
-    def capture_key(self, host):
-        return ("latent_attention",)
+    # From this many tokens on a bfloat16 step runs the two per-head maps as batched library products (the tensor
+    # cores); below, on the engine's own kernel, which streams each head's matrix once per token.
+    BATCHED_FROM = 65
 
-    def matrix_flops_per_token(self) -> float:
-        return super().matrix_flops_per_token()
+    def _tensor_core_form(self, dtype: torch.dtype) -> bool:
+        return dtype == torch.bfloat16 and ops.mma_supports(self.r, self.p)
+
+    def capture_key(self, host):
+        # the exact kernel launches the same for every step; the tensor-core one sizes its grid by the longest portion
+        return ("latent_attention", host.max_q_len)
 
     def mixing_flops(self, q_len: int, ctx_before: int) -> float:
         keys = sum(min(ctx_before + t + 1, self.window or (ctx_before + t + 1)) for t in range(q_len)) if self.window \
@@ -117,9 +124,27 @@ class LatentAttention(Mixer, Projected):
                            float(pos.magnitude) if pos is not None else 1.0, qc, cache.k, table, ctx.positions,
                            ctx.req_of_token, bad_flag=ctx.error_flag)
         q = z[:, self.q_off:self.q_off + nh * (d + p)].unflatten(1, (nh, d + p))
-        ops.head_project(q[:, :, :d], self.uk_t, qc[:, :, :r], req_of_token=ctx.req_of_token)
-        mixed = ops.latent_attention_exact(qc, cache.k, ctx.positions, ctx.req_of_token, table, r, self.scale, self.window)
         gate = z[:, self.g_off:self.g_off + nh * e] if self.gate else None
+        tensor_cores = self._tensor_core_form(z.dtype)
+        if tensor_cores and n >= self.BATCHED_FROM:
+            # absorbed queries, attention and values head-major [H, N, .] in bfloat16: the operands of batched products
+            q_lat = torch.bmm(q[:, :, :d].transpose(0, 1), self.uk)                       # [H, N, r]
+            mixed = torch.empty((nh, n, r), dtype=z.dtype, device=z.device)
+            ops.latent_attention_mma(q_lat.transpose(0, 1), qc[:, :, r:], mixed.transpose(0, 1), cache.k, ctx.positions,
+                                     ctx.q_start, table, ctx.n_requests, ctx.host.max_q_len, self.scale, self.window)
+            o = torch.bmm(mixed, self.uv_t)                                               # [H, N, e]
+            if gate is not None:
+                ops.sigmoid_gate(o.transpose(0, 1), gate, y)
+            else:
+                y.unflatten(1, (nh, e)).copy_(o.transpose(0, 1))
+            return
+        ops.head_project(q[:, :, :d], self.uk_t, qc[:, :, :r], req_of_token=ctx.req_of_token)
+        if tensor_cores:
+            mixed = torch.empty((n, nh, r), dtype=torch.float32, device=z.device)
+            ops.latent_attention_mma(qc[:, :, :r], qc[:, :, r:], mixed, cache.k, ctx.positions, ctx.q_start, table,
+                                     ctx.n_requests, ctx.host.max_q_len, self.scale, self.window)
+        else:
+            mixed = ops.latent_attention_exact(qc, cache.k, ctx.positions, ctx.req_of_token, table, r, self.scale, self.window)
         ops.head_project(mixed, self.uv, y.unflatten(1, (nh, e)), gate=gate, req_of_token=ctx.req_of_token)
 
     def forward(self, x: torch.Tensor, ctx, cache: PagedKVCache) -> torch.Tensor:
