@@ -6,6 +6,7 @@ Llama-3-8B shape (random weights, bfloat16, page size 16), batch 8, 1,024-token 
     python bench.py --impl reference                            # the reference arm (baseline/reference_arm.py)
     python bench.py --workload mixed-1b | serve-3b              # the other workloads, one JSON line each
     python bench.py --workload mixers [--sizes 1b,3b]           # Tirezen beside the Llama shape of equal size
+    python bench.py --workload mixers --family vepivik          # the same for Vepivik
 
 A "step" is one decode step of the whole batch.  ``value`` is decoded tokens per second
 with the K steps timed on the device (CUDA events) and the chosen tokens fed back on
@@ -33,8 +34,10 @@ calls (defaults 2 and 3; the median call is reported).
 delta rule, and retention) and the Llama preset of the same width: a 2,048-token prefill (also four such prompts in one step) and decode
 steps at batch 8 and 64 after 1,024-token prompts, each with its fraction of the roofline (prefill:
 matrix and mixing flops over the measured bf16 peak; decode: weights, keys and per-request state
-over the measured copy bandwidth).  ``value`` is Tirezen's decode tokens per second at batch 8 of
-the first size.
+over the measured copy bandwidth; of a routed feed-forward the experts that random routing is expected to
+choose, of a windowed layer no more keys than its window).  ``value`` is the family's decode tokens per second at
+batch 8 of the first size.  ``--family vepivik`` runs the Vepivik presets (windowed attention, attention over a
+cached latent, routed experts) beside the same Llama shapes.
 """
 
 from __future__ import annotations
@@ -279,7 +282,8 @@ def run_mixers(args) -> int:
     from yalis_b200.ops import _lib
 
     peaks, peak_source = load_peaks()
-    pairs = {"1b": ("tirezen-1b", "Llama-3.2-1B"), "3b": ("tirezen-3b", "Llama-3.2-3B")}
+    family = args.family
+    pairs = {"1b": (f"{family}-1b", "Llama-3.2-1B"), "3b": (f"{family}-3b", "Llama-3.2-3B")}
     steps = args.steps or 64
     warm = max(3, args.warmup or 8)
     batches = (8, 64)
@@ -308,14 +312,14 @@ def run_mixers(args) -> int:
                 bench = DecodeBench(engine, b, PROMPT_LEN, seed=b)
                 bench.prepare()
                 bench.run(warm)
-                first = name.startswith("tirezen") and b == batches[0] and clocks is None
+                first = name.startswith(family) and b == batches[0] and clocks is None
                 if first:
                     with ClockSampler() as cs:
                         ms = bench.run_timed(steps)
                     clocks, launches = cs.summary(), bench.launches_per_step * steps
                 else:
                     ms = bench.run_timed(steps)
-                step_bytes = (numbers["weight_bytes_per_step"] + b * bench.mean_context(steps) * numbers["kv_bytes_per_token"]
+                step_bytes = (numbers["weight_bytes_for"](b) + b * numbers["kv_bytes_at"](bench.mean_context(steps))
                               + b * numbers["state_bytes_per_request"])
                 rec[f"decode_b{b}"] = {"ms_per_step": round(ms / steps, 4), "tok_s": round(b * steps / (ms / 1e3), 1),
                                        "launches_per_step": bench.launches_per_step,
@@ -328,7 +332,7 @@ def run_mixers(args) -> int:
     first_size = args.sizes.split(",")[0]
     main_r = out[first_size][pairs[first_size][0]]["decode_b8"]
     print(json.dumps({
-        "metric": f"decode tok/s (Tirezen {first_size} shape, batch 8, {PROMPT_LEN}-token prompts)", "value": main_r["tok_s"],
+        "metric": f"decode tok/s ({family.capitalize()} {first_size} shape, batch 8, {PROMPT_LEN}-token prompts)", "value": main_r["tok_s"],
         "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warm, "ms_per_step": main_r["ms_per_step"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "impl": "ours", "workload": "mixers",
         "data": "synthetic: uniform random token ids, random weights", "models": out, "clocks": clocks,
@@ -346,6 +350,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode-8b", choices=["decode-8b", "mixed-1b", "serve-3b", "mixers"])
     ap.add_argument("--sizes", default="1b,3b", help="for --workload mixers: which pairs of models to run")
+    ap.add_argument("--family", default="tirezen", choices=["tirezen", "vepivik"],
+                    help="for --workload mixers: the family whose presets run beside the Llama shapes")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--page-size", type=int, default=None, help="tokens per cache page (default: 16 as the benchmark "
                     "configuration states for decode-8b, the engine's 64 for the other workloads)")

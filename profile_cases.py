@@ -4,6 +4,7 @@
     python profile_cases.py gemm_wstream --tokens 8 --n 28672 --k 4096 --launches 8
     python profile_cases.py recurrence --requests 1 --tokens 2048        # the state-keeping mixers' kernels
     python profile_cases.py prefill --preset tirezen-1b --layers 3 --tokens 2048
+    python profile_cases.py decode --preset vepivik-1b --layers 4 --batch 8 --ctx 1024
 
 Each case allocates inputs larger than the L2 cache but at most a few GB, launches the
 kernel a few times, and prints the mean time per launch measured with CUDA events.
@@ -233,6 +234,28 @@ def prefill(args) -> None:
           f"{args.tokens / ms * 1e3:.0f} tokens/s")
 
 
+def decode(args) -> None:
+    """Decode steps of ``--batch`` requests with ``--ctx`` cached tokens through the whole engine (``--layers`` layers of
+    the preset), replayed from a recording as generation does."""
+    from yalis_b200.bench_support import DecodeBench
+    from yalis_b200.config.presets import preset
+    from yalis_b200.engine.engine import Engine
+    cfg = preset(args.preset)
+    if args.layers and "num_hidden_layers" in cfg:
+        cfg["num_hidden_layers"] = args.layers
+    elif args.layers:
+        cfg["layers"] = cfg["layers"][:args.layers]
+    steps = args.launches
+    engine = Engine(config=cfg, seed=0, dtype=args.dtype, page_size=64, cache_tokens=args.batch * (args.ctx + steps + 80),
+                    max_slots=args.batch, max_context=args.ctx + steps + 80, max_tokens_per_step=max(2048, args.ctx))
+    bench = DecodeBench(engine, args.batch, args.ctx, settle_seconds=0.2)
+    bench.prepare()
+    bench.run(4)
+    ms = bench.run_timed(steps)
+    print(f"decode {args.preset} layers {len(engine.spec.schedule)} batch {args.batch} ctx {args.ctx} {args.dtype}: "
+          f"{ms / steps * 1e3:.1f} us a step, {bench.launches_per_step} launches a step")
+
+
 def recurrence(args) -> None:
     """The kernels of the state-keeping mixers at one layer's shape: ``--requests`` requests of ``--tokens`` tokens each
     (1 token: a decode step).  Launched one by one with the L2 written over between launches; median of ``--launches``."""
@@ -350,6 +373,14 @@ def main() -> None:
     pf.add_argument("--tokens", type=int, default=2048)
     pf.add_argument("--dtype", default="bfloat16")
     pf.add_argument("--launches", type=int, default=2)
+    dc = sub.add_parser("decode")
+    dc.add_argument("--preset", default="Llama-3.2-1B")
+    dc.add_argument("--layers", type=int, default=4)
+    dc.add_argument("--batch", type=int, default=8)
+    dc.add_argument("--ctx", type=int, default=1024)
+    dc.add_argument("--dtype", default="bfloat16")
+    dc.add_argument("--launches", type=int, default=8, help="timed steps")
+    dc.set_defaults(fn=decode)
     pf.set_defaults(fn=prefill)
     rc = sub.add_parser("recurrence")
     rc.add_argument("--requests", type=int, default=1)

@@ -211,11 +211,19 @@ def test_latent_attention_on_the_tensor_cores(r, p, page, window, heads):
     q_start, table = i32([0, new[0], n]), table.to(DEV)
     out32 = torch.zeros(n, heads, r, device=DEV)
     qd = qc.to(DEV)
-    latent_attention_mma(qd[:, :, :r], qd[:, :, r:], out32, pool, i32(positions), q_start, table, 2, max(new), 0.5, window)
+    req = i32([0] * new[0] + [1])
+    latent_attention_mma(qd[:, :, :r], qd[:, :, r:], out32, pool, i32(positions), q_start, req, table, 2, max(new), 0.5, window)
     q_lat = qc[:, :, :r].to(torch.bfloat16).transpose(0, 1).contiguous().to(DEV)            # [H, N, r]
     out16 = torch.zeros(heads, n, r, dtype=torch.bfloat16, device=DEV)
     latent_attention_mma(q_lat.transpose(0, 1), qd[:, :, r:].contiguous(), out16.transpose(0, 1), pool, i32(positions), q_start,
-                         table, 2, max(new), 0.5, window)
+                         req, table, 2, max(new), 0.5, window)
+    # single tokens of both requests (the last of each), their rows dealt to 1, 3 and 16 blocks
+    last = [new[0] - 1, n - 1]
+    for splits in (1, 3, 16):
+        one = torch.zeros(2, heads, r, device=DEV)
+        latent_attention_mma(qd[last][:, :, :r], qd[last][:, :, r:], one, pool, i32([positions[j] for j in last]), i32([0, 1, 2]),
+                             i32([0, 1]), table, 2, 1, 0.5, window, n_splits=splits)
+        torch.testing.assert_close(one, out32[last], rtol=1e-4, atol=1e-4, msg=lambda m: f"{splits} splits: {m}")
     for j, a in enumerate(positions):
         which = 0 if j < new[0] else 1
         for h in range(heads):

@@ -26,9 +26,14 @@ def model_numbers(engine: Engine) -> Dict[str, object]:
     weight_bytes = m.weight_bytes() - (0 if tied else emb_bytes)
     kv_per_token = 0
     state_per_request = 0          # bytes of per-request state a decode step reads and writes back
+    paged = []                     # (bytes per cached token, how many tokens back a query of the layer sees) per layer run
     for req, entry in zip(m.cache_requests(), engine.spec.schedule):
+        for leaf in cache_leaves(req):
+            if isinstance(leaf, PagedKV):
+                mixer = m.blocks[entry.layer].parts.get("mixer")
+                paged.append((leaf.num_kv_heads * (leaf.head_dim + leaf.value_dim) * elt, getattr(mixer, "window", leaf.window)))
         if entry.cache_of is not None:
-            continue
+            continue               # reads what another entry keeps: counted above as read, not below as kept
         for leaf in cache_leaves(req):
             if isinstance(leaf, PagedKV):
                 kv_per_token += leaf.num_kv_heads * (leaf.head_dim + leaf.value_dim) * elt
@@ -49,8 +54,21 @@ def model_numbers(engine: Engine) -> Dict[str, object]:
         """One prompt of ``tokens`` tokens from an empty cache, logits at ``logit_rows`` places."""
         return tokens * matrix_flops + sum(mx.mixing_flops(tokens, 0) for mx in mixers) + 2.0 * logit_rows * head_params
 
+    routed = [part for entry in engine.spec.schedule for part in m.blocks[entry.layer].parts.values()
+              if hasattr(part, "expected_unused_bytes")]
+
+    def weight_bytes_for(tokens: int) -> float:
+        """Weight bytes a step of ``tokens`` tokens reads: of a routed feed-forward only the experts that uniformly
+        random routing is expected to choose."""
+        return weight_bytes - sum(part.expected_unused_bytes(tokens) for part in routed)
+
+    def kv_bytes_at(context: float) -> float:
+        """Cache bytes one single-token query reads with ``context`` tokens cached: per layer run no more than its window."""
+        return sum(per_token * (context if window is None else min(context, window)) for per_token, window in paged)
+
     return {"weight_bytes_per_step": weight_bytes, "kv_bytes_per_token": kv_per_token, "flops_prefill": flops_prefill,
-            "matrix_flops_per_token": matrix_flops, "state_bytes_per_request": state_per_request}
+            "matrix_flops_per_token": matrix_flops, "state_bytes_per_request": state_per_request,
+            "weight_bytes_for": weight_bytes_for, "kv_bytes_at": kv_bytes_at}
 
 
 SETTLE_SECONDS = 1.0     # idle time between the prompt phase and the decode steps of DecodeBench

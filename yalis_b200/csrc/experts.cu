@@ -1,8 +1,8 @@
 // A routed feed-forward (mixture of experts): every token runs `top` of E small feed-forwards and adds their
 // results with weights from a router.
 //
-//   route_topk     scores = softmax(logits) over all experts (float32), the `top` largest, their scores divided
-//                  by their sum (+ eps); ties go to the smaller index.
+//   route          logits = W x in float32, scores = softmax(logits) over all experts, the `top` largest, their
+//                  scores divided by their sum (+ eps); ties go to the smaller index.  (`route_topk`: from given logits.)
 //   expert_plan    sorts the (token, choice) entries by expert: offsets per expert, a permutation slot -> entry and
 //                  its inverse, and the list of row tiles (expert, first slot) that the products walk.  The order
 //                  of entries inside an expert is whatever the atomics give; no result depends on it, since every
@@ -21,29 +21,17 @@ namespace {
 constexpr int kMaxExperts = 1024;
 constexpr int kMaxTop = 32;
 
-// One warp per token.
-__global__ void route_topk_kernel(const float* __restrict__ logits, int E, int top, float eps,
-                                  const int32_t* __restrict__ req_of_token, int32_t* __restrict__ ids,
-                                  float* __restrict__ weights, int n_tokens) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (n >= n_tokens) return;
-  if (req_of_token && req_of_token[n] < 0) {
-    for (int j = lane; j < top; j += 32) {
-      ids[(size_t)n * top + j] = -1;
-      weights[(size_t)n * top + j] = 0.f;
-    }
-    return;
-  }
+// The choice of one token by one warp: softmax over `logit(e)`, the `top` largest, renormalised.
+template <typename F>
+__device__ __forceinline__ void choose_experts(F logit, int E, int top, float eps, int lane, int32_t* __restrict__ ids,
+                                               float* __restrict__ weights) {
   constexpr int kPer = kMaxExperts / 32;
   float s[kPer];
-  const float* z = logits + (size_t)n * E;
   float m = -INFINITY;
 #pragma unroll
   for (int i = 0; i < kPer; ++i) {
     const int e = lane + 32 * i;
-    s[i] = e < E ? z[e] : -INFINITY;
+    s[i] = e < E ? logit(e) : -INFINITY;
     m = fmaxf(m, s[i]);
   }
   m = warp_max(m);
@@ -89,9 +77,60 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int E, int t
     total += best;                       // the same on every lane, in the order of the choices
   }
   if (lane < top) {
-    ids[(size_t)n * top + lane] = chosen_e;
-    weights[(size_t)n * top + lane] = chosen_w / (total + eps);
+    ids[lane] = chosen_e;
+    weights[lane] = chosen_w / (total + eps);
   }
+}
+
+// From given logits: one warp per token.
+__global__ void route_topk_kernel(const float* __restrict__ logits, int E, int top, float eps,
+                                  const int32_t* __restrict__ req_of_token, int32_t* __restrict__ ids,
+                                  float* __restrict__ weights, int n_tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (n >= n_tokens) return;
+  if (req_of_token && req_of_token[n] < 0) {
+    for (int j = lane; j < top; j += 32) {
+      ids[(size_t)n * top + j] = -1;
+      weights[(size_t)n * top + j] = 0.f;
+    }
+    return;
+  }
+  const float* z = logits + (size_t)n * E;
+  choose_experts([&](int e) { return z[e]; }, E, top, eps, lane, ids + (size_t)n * top, weights + (size_t)n * top);
+}
+
+// The router whole: logits = W x in float32 (x may be bfloat16; sums per lane in k order, then a fixed butterfly) and
+// the choice, one block per token.  The token's row waits in shared memory as float32; warps share out the experts.
+template <typename T>
+__global__ void route_kernel(const T* __restrict__ x, long x_stride, const float* __restrict__ w, int E, int K, int top,
+                             float eps, const int32_t* __restrict__ req_of_token, int32_t* __restrict__ ids,
+                             float* __restrict__ weights) {
+  extern __shared__ float route_smem[];   // [K] the row, then [E] the logits
+  float* xs = route_smem;
+  float* z = route_smem + K;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int n = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  if (req_of_token && req_of_token[n] < 0) {
+    for (int j = threadIdx.x; j < top; j += blockDim.x) {
+      ids[(size_t)n * top + j] = -1;
+      weights[(size_t)n * top + j] = 0.f;
+    }
+    return;
+  }
+  for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_f32<T>(x[(size_t)n * x_stride + k]);
+  __syncthreads();
+  for (int e = warp; e < E; e += warps) {
+    const float* wr = w + (size_t)e * K;
+    float acc = 0.f;
+    for (int k = lane; k < K; k += 32) acc = __fmaf_rn(wr[k], xs[k], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) z[e] = acc;
+  }
+  __syncthreads();
+  if (warp == 0) choose_experts([&](int e) { return z[e]; }, E, top, eps, lane, ids + (size_t)n * top, weights + (size_t)n * top);
 }
 
 // One block.  entries = n_tokens * top.  tiles: (expert, first slot) per row tile of `bm` slots, ended by n_tiles.
@@ -318,7 +357,7 @@ __global__ void expert_combine_kernel(const T* __restrict__ y, long y_stride, co
   pdl_launch_dependents();
   pdl_wait();
   const int n = blockIdx.x;
-  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < cols; c += gridDim.y * blockDim.x) {
     float acc = 0.f;
     for (int j = 0; j < top; ++j) {
       const int slot = inv[(size_t)n * top + j];
@@ -327,6 +366,45 @@ __global__ void expert_combine_kernel(const T* __restrict__ y, long y_stride, co
     if (shared) acc += to_f32<T>(shared[(size_t)n * shared_stride + c]);
     out[(size_t)n * out_stride + c] = from_f32<T>(acc);
   }
+}
+
+// The same for bfloat16 rows on 16-byte boundaries: 8 columns a thread, the same order of sums per column.
+__global__ void expert_combine_bf16x8_kernel(const __nv_bfloat16* __restrict__ y, long y_stride, const int32_t* __restrict__ inv,
+                                             const float* __restrict__ weights, int top, const __nv_bfloat16* __restrict__ shared,
+                                             long shared_stride, __nv_bfloat16* __restrict__ out, long out_stride, int cols) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int n = blockIdx.x, c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (c >= cols) return;
+  float acc[8] = {};
+  for (int j = 0; j < top; ++j) {
+    const int slot = inv[(size_t)n * top + j];
+    if (slot < 0) continue;
+    const float wj = weights[(size_t)n * top + j];
+    const uint4 raw = *reinterpret_cast<const uint4*>(y + (size_t)slot * y_stride + c);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 v = __bfloat1622float2(h[i]);
+      acc[2 * i] = __fmaf_rn(wj, v.x, acc[2 * i]);
+      acc[2 * i + 1] = __fmaf_rn(wj, v.y, acc[2 * i + 1]);
+    }
+  }
+  if (shared) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(shared + (size_t)n * shared_stride + c);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 v = __bfloat1622float2(h[i]);
+      acc[2 * i] += v.x;
+      acc[2 * i + 1] += v.y;
+    }
+  }
+  uint4 res;
+  __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) o[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+  *reinterpret_cast<uint4*>(out + (size_t)n * out_stride + c) = res;
 }
 
 }  // namespace
@@ -338,6 +416,30 @@ YALIS_API int yalis_route_topk(const float* logits, int n_tokens, int E, int top
   const int warps = 4;
   return yalis_launch(route_topk_kernel, dim3((n_tokens + warps - 1) / warps), dim3(32 * warps), 0, stream, logits, E, top,
                       eps, req_of_token, ids, weights, n_tokens);
+}
+
+// The router and the choice in one launch.  x: [n_tokens, K] float32 or bfloat16; w: float32 [E, K].
+YALIS_API int yalis_route(const void* x, int x_dtype, long x_stride, const float* w, int n_tokens, int E, int K, int top, float eps,
+                          const int32_t* req_of_token, int32_t* ids, float* weights, cudaStream_t stream) {
+  if (n_tokens <= 0) return YALIS_OK;
+  if (E <= 0 || E > kMaxExperts || top <= 0 || top > kMaxTop || top > E || K <= 0 || (size_t)(K + E) * 4 > 200 * 1024)
+    return YALIS_ERR_SHAPE;
+  const size_t smem = (size_t)(K + E) * sizeof(float);
+  if (smem > 48 * 1024) {
+    static size_t configured[2] = {0, 0};
+    const int which = x_dtype == YALIS_BF16 ? 1 : 0;
+    if (smem > configured[which]) {
+      const cudaError_t err = which ? cudaFuncSetAttribute(route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                                    : cudaFuncSetAttribute(route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (err != cudaSuccess) return YALIS_ERR_LAUNCH;
+      configured[which] = smem;
+    }
+  }
+  const int threads = E >= 8 ? 256 : 128;
+  YALIS_DISPATCH_DTYPE(x_dtype, T,
+                       return yalis_launch(route_kernel<T>, dim3(n_tokens), dim3(threads), smem, stream, (const T*)x, x_stride, w, E,
+                                           K, top, eps, req_of_token, ids, weights));
+  return YALIS_OK;
 }
 
 YALIS_API int yalis_expert_plan(const int32_t* ids, int entries, int E, int bm, int32_t* offsets, int32_t* perm,
@@ -377,8 +479,15 @@ YALIS_API int yalis_expert_combine(const void* y, long y_stride, const int32_t* 
                                    int n_tokens, int cols, cudaStream_t stream) {
   if (n_tokens <= 0 || cols <= 0) return YALIS_OK;
   if (top <= 0) return YALIS_ERR_SHAPE;
+  const bool aligned = dtype == YALIS_BF16 && cols % 8 == 0 && y_stride % 8 == 0 && out_stride % 8 == 0 && shared_stride % 8 == 0 &&
+                       !((uintptr_t)y & 15) && !((uintptr_t)out & 15) && !((uintptr_t)shared & 15);
+  if (aligned)
+    return yalis_launch(expert_combine_bf16x8_kernel, dim3(n_tokens, (cols / 8 + 127) / 128), dim3(128), 0, stream,
+                        (const __nv_bfloat16*)y, y_stride, inv, weights, top, (const __nv_bfloat16*)shared, shared_stride,
+                        (__nv_bfloat16*)out, out_stride, cols);
+  const int col_blocks = (cols + 1023) / 1024;
   YALIS_DISPATCH_DTYPE(dtype, T,
-                       return yalis_launch(expert_combine_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (const T*)y,
+                       return yalis_launch(expert_combine_kernel<T>, dim3(n_tokens, col_blocks), dim3(256), 0, stream, (const T*)y,
                                            y_stride, inv, weights, top, (const T*)shared, shared_stride, (T*)out,
                                            out_stride, cols));
   return YALIS_OK;

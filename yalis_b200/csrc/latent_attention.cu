@@ -103,14 +103,22 @@ __global__ void head_project_kernel(const TX* __restrict__ x, long xs_n, long xs
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const T* wh = w + (size_t)h * O * K;
-  for (int o = warp; o < O; o += warps) {
-    const T* wr = wh + (size_t)o * K;
-    float acc = 0.f;
-    for (int k = lane; k < K; k += 32) acc = __fmaf_rn(to_f32<T>(wr[k]), xs[k], acc);
-    acc = warp_sum(acc);
-    if (lane == 0) {
-      if (gate) acc *= 1.0f / (1.0f + expf(-to_f32<T>(gate[(size_t)n * gs_n + (size_t)h * O + o])));
-      out[(size_t)n * os_n + (size_t)h * os_h + o] = from_f32<TO>(acc);
+  // four outputs in flight per warp: their loads and butterflies overlap; each output's own order of sums is fixed
+  for (int o0 = warp * 4; o0 < O; o0 += warps * 4) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k = lane; k < K; k += 32) {
+      const float xv = xs[k];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (o0 + j < O) acc[j] = __fmaf_rn(to_f32<T>(wh[(size_t)(o0 + j) * K + k]), xv, acc[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[j] = warp_sum(acc[j]);
+    if (lane < 4 && o0 + lane < O) {
+      const int o = o0 + lane;
+      float v = lane == 0 ? acc[0] : (lane == 1 ? acc[1] : (lane == 2 ? acc[2] : acc[3]));
+      if (gate) v *= 1.0f / (1.0f + expf(-to_f32<T>(gate[(size_t)n * gs_n + (size_t)h * O + o])));
+      out[(size_t)n * os_n + (size_t)h * os_h + o] = from_f32<TO>(v);
     }
   }
 }
@@ -217,14 +225,16 @@ __global__ void latent_attention_exact_kernel(const float* __restrict__ qc, floa
 
 // ---- the tensor-core attention ------------------------------------------------------------------------------------------
 // bfloat16 rows, mma.sync.m16n8k16 with float32 accumulators.  All heads of a token read the same rows, so a tile
-// of 32 query rows is (tokens x heads) of one request in token order: a decode step fills it with the heads of one
-// token, a prompt portion with several tokens.  A block walks the rows its tile can see 64 at a time (cp.async, two
-// buffers, a page lookup per row).  Per 64 rows: each of the 4 warps computes the scores of 16 of them for all 32
-// queries (K = r + p), the row maxima meet in shared memory, the weights exp(s - m) go to shared memory as TWO
-// bfloat16 halves (rounding and rounding of the rest: 16 bits of mantissa, since weights are 32-bit by the design's
-// rule), and each warp then adds weights x rows[:, its quarter of the r columns] to its accumulators (the rows are
-// the B operand through ldmatrix.trans).  Maxima, sums and accumulators are float32.
-constexpr int kQRows = 32, kKeyTile = 64;
+// of 32 or 64 query rows is (tokens x heads) of one request in token order: a decode step fills it with the heads of
+// one token, a prompt portion with several tokens.  A block walks the rows its tile can see 64 at a time (cp.async,
+// two buffers, a page lookup per row).  Per 64 rows and group of 32 queries (4 warps): each warp computes the scores
+// of 16 rows for the 32 queries (K = r + p), the row maxima meet in shared memory, the weights exp(s - m) go to
+// shared memory as TWO bfloat16 halves (rounding and rounding of the rest: 16 bits of mantissa, since weights are
+// 32-bit by the design's rule), and each warp then adds weights x rows[:, its quarter of the r columns] to its
+// accumulators (the rows are the B operand through ldmatrix.trans).  Maxima, sums and accumulators are float32.
+// In steps of single tokens the 64-row tiles of a request are dealt to `n_splits` blocks in turn (z of the grid);
+// each leaves its unnormalised sums, maximum and sum of weights, which `latent_merge` adds in the order of z.
+constexpr int kKeyTile = 64;
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
   const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -246,31 +256,35 @@ struct LatentMma {
   const int32_t* positions; const int32_t* q_start;
   const int32_t* block_table; int table_width, page_size, num_pages;
   int heads, p; float scale; int window;
+  int n_splits; float* part_o; float* part_ml;          // [splits, tokens * heads, r] and [.., 2] when n_splits > 1
+  int n_tokens;
 };
 
-template <int R>
-__global__ void __launch_bounds__(128) latent_attention_mma_kernel(const LatentMma a) {
+template <int R, int WR>                            // WR groups of 32 queries (4 warps each) share the rows they read
+__global__ void __launch_bounds__(128 * WR) latent_attention_mma_kernel(const LatentMma a) {
   constexpr int NT = R / 32;                       // 8-column tiles of the output a warp owns
+  constexpr int BM = 32 * WR, THREADS = 128 * WR, TPR = THREADS / kKeyTile;   // threads per row of a tile of keys
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int W = R + a.p, LD = W + 8;               // rows of (W + 8) * 2 bytes: fragment loads hit 32 distinct banks
   constexpr int LDP = kKeyTile + 8;
-  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [32][LD]
-  __nv_bfloat16* Ks = Qs + kQRows * LD;                                      // [2][64][LD]
-  __nv_bfloat16* Ph = Ks + 2 * kKeyTile * LD;                                // [32][LDP]
-  __nv_bfloat16* Pl = Ph + kQRows * LDP;                                     // [32][LDP]
-  float* red = reinterpret_cast<float*>(Pl + kQRows * LDP);                  // [4][32]
-  int* row_pos = reinterpret_cast<int*>(red + 4 * kQRows);                   // [32]
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [BM][LD]
+  __nv_bfloat16* Ks = Qs + BM * LD;                                          // [2][64][LD]
+  __nv_bfloat16* Ph = Ks + 2 * kKeyTile * LD;                                // [BM][LDP]
+  __nv_bfloat16* Pl = Ph + BM * LDP;                                         // [BM][LDP]
+  float* red = reinterpret_cast<float*>(Pl + BM * LDP);                      // [4][BM]
+  int* row_pos = reinterpret_cast<int*>(red + 4 * BM);                       // [BM]
   pdl_launch_dependents();
   pdl_wait();
   const int req = blockIdx.y;
   const int q0 = a.q_start[req], q_len = a.q_start[req + 1] - q0;
-  const int n_rows = q_len * a.heads, row0 = blockIdx.x * kQRows;
+  const int n_rows = q_len * a.heads, row0 = blockIdx.x * BM;
   if (row0 >= n_rows) return;
-  const int rows_here = min(kQRows, n_rows - row0);
+  const int rows_here = min(BM, n_rows - row0);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gq = lane >> 2, tq = lane & 3;
+  const int wc = warp & 3, rb = (warp >> 2) * 32;  // this warp's quarter of keys / columns, its group's first query
 
   // the tile's queries as bfloat16, and each row's position
-  for (int i = tid; i < kQRows * W; i += 128) {
+  for (int i = tid; i < BM * W; i += THREADS) {
     const int r = i / W, c = i - r * W;
     float v = 0.f;
     if (r < rows_here) {
@@ -284,18 +298,19 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(const LatentM
     }
     Qs[r * LD + c] = __float2bfloat16_rn(v);
   }
-  if (tid < kQRows) row_pos[tid] = tid < rows_here ? a.positions[q0 + (row0 + tid) / a.heads] : -1;
+  if (tid < BM) row_pos[tid] = tid < rows_here ? a.positions[q0 + (row0 + tid) / a.heads] : -1;
   const int pos_first = a.positions[q0 + row0 / a.heads];
   const int pos_last = a.positions[q0 + (row0 + rows_here - 1) / a.heads];
   const int lo = (a.window > 0 && pos_first - a.window + 1 > 0) ? pos_first - a.window + 1 : 0;
   const int n_tiles = (pos_last - lo) / kKeyTile + 1;
   const int32_t* bt = a.block_table + (size_t)req * a.table_width;
   const int chunks = W / 8;
+  const int step = a.n_splits, tile_first = blockIdx.z;
 
-  auto load = [&](int tile) {
-    // two threads per row: one page lookup each, then alternate 16-byte pieces
-    __nv_bfloat16* dst = Ks + (size_t)(tile & 1) * kKeyTile * LD;
-    const int r = tid >> 1, j = lo + tile * kKeyTile + r;
+  auto load = [&](int tile, int buf) {
+    // TPR threads per row: one page lookup each, then 16-byte pieces in turn
+    __nv_bfloat16* dst = Ks + (size_t)buf * kKeyTile * LD;
+    const int r = tid / TPR, j = lo + tile * kKeyTile + r;
     const __nv_bfloat16* src = a.pool;
     bool ok = j <= pos_last;
     if (ok) {
@@ -304,7 +319,7 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(const LatentM
       ok = page >= 0 && page < a.num_pages;
       if (ok) src = a.pool + ((size_t)page * a.page_size + (j - pi * a.page_size)) * W;
     }
-    for (int ch = tid & 1; ch < chunks; ch += 2) cp_async_16(dst + r * LD + ch * 8, ok ? src + ch * 8 : a.pool, ok);
+    for (int ch = tid % TPR; ch < chunks; ch += TPR) cp_async_16(dst + r * LD + ch * 8, ok ? src + ch * 8 : a.pool, ok);
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
 
@@ -318,19 +333,20 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(const LatentM
       l_run[mt][hf] = 0.f;
     }
 
-  load(0);
-  for (int tile = 0; tile < n_tiles; ++tile) {
+  if (tile_first < n_tiles) load(tile_first, 0);
+  int buf = 0;
+  for (int tile = tile_first; tile < n_tiles; tile += step, buf ^= 1) {
     asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncthreads();                                // tile `tile` is in place; everyone is done with tile - 1
-    if (tile + 1 < n_tiles) load(tile + 1);
-    const __nv_bfloat16* Kt = Ks + (size_t)(tile & 1) * kKeyTile * LD;
-    // scores of this warp's 16 rows for all 32 queries
+    __syncthreads();                                // this tile is in place; everyone is done with the one before
+    if (tile + step < n_tiles) load(tile + step, buf ^ 1);
+    const __nv_bfloat16* Kt = Ks + (size_t)buf * kKeyTile * LD;
+    // scores of this warp's 16 rows for its group's 32 queries
     float s[2][2][4] = {};
     for (int k0 = 0; k0 < W; k0 += 16) {
       uint32_t af[2][4];
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
-        const __nv_bfloat16* qp = Qs + (mt * 16 + gq) * LD + k0 + 2 * tq;
+        const __nv_bfloat16* qp = Qs + (rb + mt * 16 + gq) * LD + k0 + 2 * tq;
         af[mt][0] = *reinterpret_cast<const uint32_t*>(qp);
         af[mt][1] = *reinterpret_cast<const uint32_t*>(qp + 8 * LD);
         af[mt][2] = *reinterpret_cast<const uint32_t*>(qp + 8);
@@ -338,20 +354,19 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(const LatentM
       }
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
-        const __nv_bfloat16* kp = Kt + (warp * 16 + nt * 8 + gq) * LD + k0 + 2 * tq;
+        const __nv_bfloat16* kp = Kt + (wc * 16 + nt * 8 + gq) * LD + k0 + 2 * tq;
         const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kp), b1 = *reinterpret_cast<const uint32_t*>(kp + 8);
 #pragma unroll
         for (int mt = 0; mt < 2; ++mt) mma_bf16(s[mt][nt], af[mt], b0, b1);
       }
     }
     // mask, scale, row maxima of this warp's keys
-    const int key0 = lo + tile * kKeyTile + warp * 16;
-    float mx[2][2];
+    const int key0 = lo + tile * kKeyTile + wc * 16;
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
-        const int pos = row_pos[mt * 16 + gq + hf * 8];
+        const int pos = row_pos[rb + mt * 16 + gq + hf * 8];
         float m = -INFINITY;
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
@@ -365,8 +380,7 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(const LatentM
           }
         m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
         m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-        mx[mt][hf] = m;
-        if (tq == 0) red[warp * kQRows + mt * 16 + gq + hf * 8] = m;
+        if (tq == 0) red[wc * BM + rb + mt * 16 + gq + hf * 8] = m;
       }
     __syncthreads();
     float corr[2][2];
@@ -374,8 +388,8 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(const LatentM
     for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
-        const int r = mt * 16 + gq + hf * 8;
-        const float m_new = fmaxf(fmaxf(m_run[mt][hf], fmaxf(red[r], red[kQRows + r])), fmaxf(red[2 * kQRows + r], red[3 * kQRows + r]));
+        const int r = rb + mt * 16 + gq + hf * 8;
+        const float m_new = fmaxf(fmaxf(m_run[mt][hf], fmaxf(red[r], red[BM + r])), fmaxf(red[2 * BM + r], red[3 * BM + r]));
         corr[mt][hf] = m_new == -INFINITY ? 1.f : expf(m_run[mt][hf] - m_new);
         m_run[mt][hf] = m_new;
         float sum = 0.f;
@@ -390,7 +404,7 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(const LatentM
           }
           const __nv_bfloat162 hi = __floats2bfloat162_rn(pv[0], pv[1]);
           const __nv_bfloat162 lw = __floats2bfloat162_rn(pv[0] - __bfloat162float(hi.x), pv[1] - __bfloat162float(hi.y));
-          const int c = warp * 16 + nt * 8 + 2 * tq;
+          const int c = wc * 16 + nt * 8 + 2 * tq;
           *reinterpret_cast<__nv_bfloat162*>(Ph + r * LDP + c) = hi;
           *reinterpret_cast<__nv_bfloat162*>(Pl + r * LDP + c) = lw;
         }
@@ -414,7 +428,7 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(const LatentM
       uint32_t ah[2][4], al[2][4];
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
-        const int off = (mt * 16 + gq) * LDP + kk + 2 * tq;
+        const int off = (rb + mt * 16 + gq) * LDP + kk + 2 * tq;
         ah[mt][0] = *reinterpret_cast<const uint32_t*>(Ph + off);
         ah[mt][1] = *reinterpret_cast<const uint32_t*>(Ph + off + 8 * LDP);
         ah[mt][2] = *reinterpret_cast<const uint32_t*>(Ph + off + 8);
@@ -427,7 +441,7 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(const LatentM
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
         // rows kk .. kk + 15 of the tile, 8 columns: lanes 0-15 name the 16 row starts
-        const __nv_bfloat16* vp = Kt + (kk + (lane & 15)) * LD + warp * (R / 4) + nt * 8;
+        const __nv_bfloat16* vp = Kt + (kk + (lane & 15)) * LD + wc * (R / 4) + nt * 8;
         uint32_t b0, b1;
         const unsigned addr = (unsigned)__cvta_generic_to_shared(vp);
         asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
@@ -445,18 +459,32 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(const LatentM
   for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
     for (int hf = 0; hf < 2; ++hf)
-      if (tq == 0) red[warp * kQRows + mt * 16 + gq + hf * 8] = l_run[mt][hf];
+      if (tq == 0) red[wc * BM + rb + mt * 16 + gq + hf * 8] = l_run[mt][hf];
   __syncthreads();
 #pragma unroll
   for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
     for (int hf = 0; hf < 2; ++hf) {
-      const int r = mt * 16 + gq + hf * 8;
+      const int r = rb + mt * 16 + gq + hf * 8;
       if (r >= rows_here) continue;
-      const float l = ((red[r] + red[kQRows + r]) + red[2 * kQRows + r]) + red[3 * kQRows + r];
-      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      const float l = ((red[r] + red[BM + r]) + red[2 * BM + r]) + red[3 * BM + r];
       const int tok = q0 + (row0 + r) / a.heads, h = (row0 + r) % a.heads;
-      const size_t base = (size_t)tok * a.o_n + (size_t)h * a.o_h + warp * (R / 4);
+      if (a.n_splits > 1) {                         // this block's share, for the merge
+        const size_t row = ((size_t)blockIdx.z * a.n_tokens + tok) * a.heads + h;
+        if (wc == 0 && tq == 0) {
+          a.part_ml[row * 2] = m_run[mt][hf];
+          a.part_ml[row * 2 + 1] = l;
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const int c = wc * (R / 4) + nt * 8 + 2 * tq;
+          a.part_o[row * R + c] = o[mt][nt][hf * 2];
+          a.part_o[row * R + c + 1] = o[mt][nt][hf * 2 + 1];
+        }
+        continue;
+      }
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      const size_t base = (size_t)tok * a.o_n + (size_t)h * a.o_h + wc * (R / 4);
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
         const float v0 = o[mt][nt][hf * 2] * inv, v1 = o[mt][nt][hf * 2 + 1] * inv;
@@ -472,18 +500,60 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(const LatentM
     }
 }
 
-template <int R>
+// out = sum_z o_z exp(m_z - M) / sum_z l_z exp(m_z - M) in the order of z.  One warp per (token, head).
+__global__ void latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int n_splits,
+                                    int n_tokens, int heads, int r, const int32_t* __restrict__ req_of_token, void* out,
+                                    int out_bf16, long o_n, long o_h) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= n_tokens * heads) return;
+  const int tok = row / heads, h = row - tok * heads;
+  if (req_of_token[tok] < 0) return;
+  float M = -INFINITY;
+  for (int z = 0; z < n_splits; ++z) M = fmaxf(M, part_ml[((size_t)z * n_tokens * heads + row) * 2]);
+  float l = 0.f;
+  for (int z = 0; z < n_splits; ++z) {
+    const float m = part_ml[((size_t)z * n_tokens * heads + row) * 2];
+    if (m != -INFINITY) l += part_ml[((size_t)z * n_tokens * heads + row) * 2 + 1] * expf(m - M);
+  }
+  const float inv = l > 0.f ? 1.0f / l : 0.f;
+  for (int c = lane; c < r; c += 32) {
+    float acc = 0.f;
+    for (int z = 0; z < n_splits; ++z) {
+      const float m = part_ml[((size_t)z * n_tokens * heads + row) * 2];
+      if (m != -INFINITY) acc += part_o[((size_t)z * n_tokens * heads + row) * r + c] * expf(m - M);
+    }
+    const size_t at = (size_t)tok * o_n + (size_t)h * o_h + c;
+    if (out_bf16) reinterpret_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(acc * inv);
+    else reinterpret_cast<float*>(out)[at] = acc * inv;
+  }
+}
+
+template <int R, int WR>
+size_t latent_mma_smem(int p) {
+  const int LD = R + p + 8;
+  return (size_t)(32 * WR + 2 * kKeyTile) * LD * 2 + 2 * (size_t)32 * WR * (kKeyTile + 8) * 2 + 5 * 32 * WR * 4;
+}
+
+template <int R, int WR>
 int launch_latent_mma(const LatentMma& a, int max_rows, int n_requests, cudaStream_t stream) {
-  const int W = R + a.p, LD = W + 8;
-  const size_t smem = (size_t)(kQRows + 2 * kKeyTile) * LD * 2 + 2 * (size_t)kQRows * (kKeyTile + 8) * 2 + 4 * kQRows * 4 + kQRows * 4;
+  const size_t smem = latent_mma_smem<R, WR>(a.p);
   static size_t configured = 0;
   if (smem > configured) {
-    if (cudaFuncSetAttribute(latent_attention_mma_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(latent_attention_mma_kernel<R, WR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return YALIS_ERR_LAUNCH;
     configured = smem;
   }
-  const dim3 grid((max_rows + kQRows - 1) / kQRows, n_requests);
-  return yalis_launch(latent_attention_mma_kernel<R>, grid, dim3(128), smem, stream, a);
+  const dim3 grid((max_rows + 32 * WR - 1) / (32 * WR), n_requests, a.n_splits);
+  return yalis_launch(latent_attention_mma_kernel<R, WR>, grid, dim3(128 * WR), smem, stream, a);
+}
+
+// Tiles of 64 queries where a step has that many rows per request and shared memory has the room, else of 32.
+template <int R>
+int launch_latent_mma_any(const LatentMma& a, int max_rows, int n_requests, cudaStream_t stream) {
+  if (max_rows > 32 && latent_mma_smem<R, 2>(a.p) <= 227 * 1024) return launch_latent_mma<R, 2>(a, max_rows, n_requests, stream);
+  return launch_latent_mma<R, 1>(a, max_rows, n_requests, stream);
 }
 
 }  // namespace
@@ -515,7 +585,7 @@ YALIS_API int yalis_head_project(const void* x, int x_dtype, long xs_n, long xs_
                                  long gs_n, const int32_t* req_of_token, int n_tokens, cudaStream_t stream) {
   if (n_tokens <= 0) return YALIS_OK;
   if (heads <= 0 || heads > 65535 || O <= 0 || K <= 0 || K > 12288) return YALIS_ERR_SHAPE;
-  const dim3 grid(n_tokens, heads), block(128);
+  const dim3 grid(n_tokens, heads), block(256);
   const size_t smem = (size_t)K * sizeof(float);
 #define YALIS_HP(T, TX, TO)                                                                                         \
   return yalis_launch(head_project_kernel<T, TX, TO>, grid, block, smem, stream, (const TX*)x, xs_n, xs_h, (const T*)w, \
@@ -566,31 +636,40 @@ YALIS_API int yalis_latent_attention_exact(const float* qc, float* out, const vo
 // (32 + 128) rows of r + p + 8 bfloat16 within an SM's shared memory.
 YALIS_API int yalis_latent_attention_mma_supports(int r, int p) {
   if (!(r == 64 || r == 96 || r == 128 || r == 256 || r == 384 || r == 512) || p < 0 || p % 16) return 0;
-  return (size_t)(kQRows + 2 * kKeyTile) * (r + p + 8) * 2 + 10240 <= 227 * 1024 ? 1 : 0;
+  return (size_t)(32 + 2 * kKeyTile) * (r + p + 8) * 2 + 10240 <= 227 * 1024 ? 1 : 0;
 }
 
 // max_q_len: the longest portion of the step (bounds the grid); q_lat / out: float32 or bfloat16 by their flags.
+// n_splits > 1 (steps of single tokens): part_o float32 [n_splits, n_tokens * heads, r], part_ml [.., 2].
 YALIS_API int yalis_latent_attention_mma(const void* q_lat, int q_lat_bf16, long ql_n, long ql_h, const float* q_rot, long qr_n,
                                          long qr_h, void* out, int out_bf16, long o_n, long o_h, const void* pool,
-                                         const int32_t* positions, const int32_t* q_start, const int32_t* block_table,
-                                         int table_width, int page_size, int num_pages, int n_requests, int max_q_len,
-                                         int heads, int r, int p, float scale, int window, cudaStream_t stream) {
+                                         const int32_t* positions, const int32_t* q_start, const int32_t* req_of_token,
+                                         const int32_t* block_table, int table_width, int page_size, int num_pages,
+                                         int n_requests, int n_tokens, int max_q_len, int heads, int r, int p, float scale,
+                                         int window, int n_splits, float* part_o, float* part_ml, cudaStream_t stream) {
   if (n_requests <= 0 || max_q_len <= 0) return YALIS_OK;
-  if (!yalis_latent_attention_mma_supports(r, p) || heads <= 0 || n_requests > 65535) return YALIS_ERR_SHAPE;
+  if (!yalis_latent_attention_mma_supports(r, p) || heads <= 0 || n_requests > 65535 || n_splits < 1 || n_splits > 65535)
+    return YALIS_ERR_SHAPE;
+  if (n_splits > 1 && (part_o == nullptr || part_ml == nullptr)) return YALIS_ERR_SHAPE;
   if ((uintptr_t)pool & 15) return YALIS_ERR_ALIGN;
   LatentMma a;
   a.q_lat = q_lat; a.q_lat_bf16 = q_lat_bf16; a.ql_n = ql_n; a.ql_h = ql_h; a.q_rot = q_rot; a.qr_n = qr_n; a.qr_h = qr_h;
   a.out = out; a.out_bf16 = out_bf16; a.o_n = o_n; a.o_h = o_h; a.pool = (const __nv_bfloat16*)pool; a.positions = positions;
   a.q_start = q_start; a.block_table = block_table; a.table_width = table_width; a.page_size = page_size;
   a.num_pages = num_pages; a.heads = heads; a.p = p; a.scale = scale; a.window = window;
+  a.n_splits = n_splits; a.part_o = part_o; a.part_ml = part_ml; a.n_tokens = n_tokens;
   const int max_rows = max_q_len * heads;
+  int status = YALIS_ERR_SHAPE;
   switch (r) {
-    case 64: return launch_latent_mma<64>(a, max_rows, n_requests, stream);
-    case 96: return launch_latent_mma<96>(a, max_rows, n_requests, stream);
-    case 128: return launch_latent_mma<128>(a, max_rows, n_requests, stream);
-    case 256: return launch_latent_mma<256>(a, max_rows, n_requests, stream);
-    case 384: return launch_latent_mma<384>(a, max_rows, n_requests, stream);
-    case 512: return launch_latent_mma<512>(a, max_rows, n_requests, stream);
+    case 64: status = launch_latent_mma_any<64>(a, max_rows, n_requests, stream); break;
+    case 96: status = launch_latent_mma_any<96>(a, max_rows, n_requests, stream); break;
+    case 128: status = launch_latent_mma_any<128>(a, max_rows, n_requests, stream); break;
+    case 256: status = launch_latent_mma_any<256>(a, max_rows, n_requests, stream); break;
+    case 384: status = launch_latent_mma_any<384>(a, max_rows, n_requests, stream); break;
+    case 512: status = launch_latent_mma_any<512>(a, max_rows, n_requests, stream); break;
   }
-  return YALIS_ERR_SHAPE;
+  if (status != YALIS_OK || n_splits == 1) return status;
+  const int rows = n_tokens * heads, warps = 4;
+  return yalis_launch(latent_merge_kernel, dim3((rows + warps - 1) / warps), dim3(32 * warps), 0, stream, (const float*)part_o,
+                      (const float*)part_ml, n_splits, n_tokens, heads, r, req_of_token, out, out_bf16, o_n, o_h);
 }

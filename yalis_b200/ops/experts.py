@@ -29,6 +29,22 @@ def route_topk(logits: torch.Tensor, top: int, eps: float = 1e-20, req_of_token:
     return ids, weights
 
 
+def route(x: torch.Tensor, router: torch.Tensor, top: int, eps: float = 1e-20, req_of_token: Optional[torch.Tensor] = None):
+    """``route_topk`` of the logits ``x router^T`` in one launch: ``x`` [N, K] (float32 or bfloat16, unit inner stride),
+    ``router`` float32 [E, K].  The logits are float32 sums in a fixed order per (token, expert)."""
+    name = "route"
+    need_cuda(name, x, router, req_of_token)
+    need(x.dim() == 2 and x.stride(1) == 1 and router.dtype == torch.float32 and router.dim() == 2 and router.is_contiguous()
+         and router.shape[1] == x.shape[1], name, "x [N, K], router contiguous float32 [E, K]")
+    n, e = x.shape[0], router.shape[0]
+    need(0 < top <= min(e, MAX_TOP) and e <= MAX_EXPERTS, name, f"needs top <= min(E, {MAX_TOP}) and E <= {MAX_EXPERTS}")
+    ids = torch.empty((n, top), dtype=torch.int32, device=x.device)
+    weights = torch.empty((n, top), dtype=torch.float32, device=x.device)
+    check(lib().yalis_route(ptr(x), i32(dtype_code(x.dtype)), i64(x.stride(0)), ptr(router), i32(n), i32(e), i32(x.shape[1]), i32(top),
+                            f32(eps), ptr(req_of_token), ptr(ids), ptr(weights), stream()), name)
+    return ids, weights
+
+
 @dataclass
 class ExpertPlan:
     """The entries (token, choice) of a step sorted by expert: ``offsets`` [E + 1], ``perm`` slot -> entry, ``inv``

@@ -120,15 +120,16 @@ def mma_supports(r: int, p: int) -> bool:
 
 
 def latent_attention_mma(q_lat: torch.Tensor, q_rot: torch.Tensor, out: torch.Tensor, pool: torch.Tensor,
-                         positions: torch.Tensor, q_start: torch.Tensor, block_table: torch.Tensor, n_requests: int,
-                         max_q_len: int, scale: float, window: Optional[int]) -> torch.Tensor:
+                         positions: torch.Tensor, q_start: torch.Tensor, req_of_token: torch.Tensor, block_table: torch.Tensor,
+                         n_requests: int, max_q_len: int, scale: float, window: Optional[int], n_splits: int = 1) -> torch.Tensor:
     """The same sums as ``latent_attention_exact`` on the tensor cores, for bfloat16 rows.  ``q_lat`` [N, H, r]
     (float32 or bfloat16) and ``q_rot`` [N, H, p] (float32) are the two parts of the queries and ``out`` [N, H, r]
     (float32 or bfloat16) the result, each with any strides over n and h and unit inner stride.  ``q_start`` int32
     [R + 1] gives each request's token range; ``max_q_len`` bounds the grid.  Queries and rows meet as bfloat16 with
-    float32 sums; the weights meet the rows in two bfloat16 halves."""
+    float32 sums; the weights meet the rows in two bfloat16 halves.  ``n_splits`` > 1 deals the rows a request's
+    queries see to that many blocks in turn and merges their shares in order (for steps of single tokens)."""
     name = "latent_attention_mma"
-    need_cuda(name, q_lat, q_rot, out, pool, positions, q_start, block_table)
+    need_cuda(name, q_lat, q_rot, out, pool, positions, q_start, req_of_token, block_table)
     n, h, r = q_lat.shape
     p = q_rot.shape[2]
     need(q_rot.shape == (n, h, p) and out.shape == (n, h, r) and q_rot.dtype == torch.float32
@@ -139,10 +140,15 @@ def latent_attention_mma(q_lat: torch.Tensor, q_rot: torch.Tensor, out: torch.Te
     need(mma_supports(r, p), name, f"r = {r}, p = {p} is not a shape of the tensor-core form")
     need(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous() and q_start.dtype == torch.int32
          and q_start.numel() >= n_requests + 1, name, "block_table int32 [R, width], q_start int32 [R + 1]")
+    need(n_splits >= 1, name, "n_splits must be positive")
+    part_o = part_ml = None
+    if n_splits > 1:
+        part_o = torch.empty((n_splits, n * h, r), dtype=torch.float32, device=q_lat.device)
+        part_ml = torch.full((n_splits, n * h, 2), float("-inf"), dtype=torch.float32, device=q_lat.device)
     check(lib().yalis_latent_attention_mma(
         ptr(q_lat), i32(q_lat.dtype == torch.bfloat16), i64(q_lat.stride(0)), i64(q_lat.stride(1)), ptr(q_rot),
         i64(q_rot.stride(0)), i64(q_rot.stride(1)), ptr(out), i32(out.dtype == torch.bfloat16), i64(out.stride(0)),
-        i64(out.stride(1)), ptr(pool), ptr(positions), ptr(q_start), ptr(block_table), i32(block_table.shape[1]),
-        i32(pool.shape[2]), i32(pool.shape[0]), i32(n_requests), i32(max_q_len), i32(h), i32(r), i32(p), f32(scale),
-        i32(window or 0), stream()), name)
+        i64(out.stride(1)), ptr(pool), ptr(positions), ptr(q_start), ptr(req_of_token), ptr(block_table), i32(block_table.shape[1]),
+        i32(pool.shape[2]), i32(pool.shape[0]), i32(n_requests), i32(n), i32(max_q_len), i32(h), i32(r), i32(p), f32(scale),
+        i32(window or 0), i32(n_splits), ptr(part_o), ptr(part_ml), stream()), name)
     return out

@@ -4,7 +4,7 @@ router, and optionally a shared one that every token runs.
     s = softmax(W_r x) over all experts (float32);  chosen = the ``top`` largest s;  w_j = s_j / (sum chosen s + eps)
     y = sum_j w_j  D_j act(U_j x)  +  D_s act(U_s x)
 
-The router's matrix is held in float32 and its product runs on the exact kernel.  The experts' products are one
+The router's matrix is held in float32 and its product, softmax and choice are one float32 kernel.  The experts' products are one
 launch each way over all experts (tokens sorted by expert on the device, nothing read back), so a step with
 routed layers launches the same kernels whatever the routing and can be recorded.
 """
@@ -69,6 +69,12 @@ class RoutedExperts(FeedForward):
         # the products a token runs: the router, ``top`` experts and the shared one
         return 2.0 * self.hidden * (self.n_experts + 2 * self.top * self.inner + 2 * (self.shared or 0))
 
+    def expected_unused_bytes(self, tokens: int) -> float:
+        """Bytes of the experts that a step of ``tokens`` tokens is expected to leave unread when every choice is
+        uniformly random (for rooflines)."""
+        unused = self.n_experts * (1.0 - self.top / self.n_experts) ** tokens
+        return unused * (self.w_up[0].numel() + self.w_down[0].numel()) * self.w_up.element_size()
+
     def row_tile(self, x: torch.Tensor) -> int:
         """Rows of a tile of the experts' products: 128 where the tensor-core form runs and an expert gets that many
         tokens on average, else 32."""
@@ -77,8 +83,7 @@ class RoutedExperts(FeedForward):
         return 128 if tc and x.shape[0] * self.top >= 96 * self.n_experts else 32
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
-        logits = linear(x, self.router, out_dtype=torch.float32)
-        ids, weights = ops.route_topk(logits, self.top, self.eps, ctx.req_of_token if ctx is not None else None)
+        ids, weights = ops.route(x, self.router, self.top, self.eps, ctx.req_of_token if ctx is not None else None)
         plan = ops.expert_plan(ids, self.n_experts, self.row_tile(x))
         inner = ops.grouped_gemm(x, self.w_up, plan, gather_top=self.top, act=_GROUPED_ACT[self.act])
         y = ops.grouped_gemm(inner, self.w_down, plan)

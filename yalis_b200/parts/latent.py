@@ -108,6 +108,15 @@ class LatentAttention(Mixer, Projected):
         # the exact kernel launches the same for every step; the tensor-core one sizes its grid by the longest portion
         return ("latent_attention", host.max_q_len)
 
+    def _splits(self, ctx) -> int:
+        """Blocks that share the rows of one request in a step of single tokens: enough to fill the GPU twice, at most
+        16 (a function of the step's shape alone, so a recording keeps it)."""
+        if ctx.host.max_q_len != 1:
+            return 1
+        from yalis_b200.ops.attention import sm_count
+        tiles = ctx.n_requests * -(-self.nh // 32)
+        return max(1, min(16, (2 * sm_count(ctx.positions.device)) // max(1, tiles)))
+
     def mixing_flops(self, q_len: int, ctx_before: int) -> float:
         keys = sum(min(ctx_before + t + 1, self.window or (ctx_before + t + 1)) for t in range(q_len)) if self.window \
             else q_len * ctx_before + q_len * (q_len + 1) / 2
@@ -131,7 +140,8 @@ class LatentAttention(Mixer, Projected):
             q_lat = torch.bmm(q[:, :, :d].transpose(0, 1), self.uk)                       # [H, N, r]
             mixed = torch.empty((nh, n, r), dtype=z.dtype, device=z.device)
             ops.latent_attention_mma(q_lat.transpose(0, 1), qc[:, :, r:], mixed.transpose(0, 1), cache.k, ctx.positions,
-                                     ctx.q_start, table, ctx.n_requests, ctx.host.max_q_len, self.scale, self.window)
+                                     ctx.q_start, ctx.req_of_token, table, ctx.n_requests, ctx.host.max_q_len, self.scale,
+                                     self.window)
             o = torch.bmm(mixed, self.uv_t)                                               # [H, N, e]
             if gate is not None:
                 ops.sigmoid_gate(o.transpose(0, 1), gate, y)
@@ -141,8 +151,9 @@ class LatentAttention(Mixer, Projected):
         ops.head_project(q[:, :, :d], self.uk_t, qc[:, :, :r], req_of_token=ctx.req_of_token)
         if tensor_cores:
             mixed = torch.empty((n, nh, r), dtype=torch.float32, device=z.device)
-            ops.latent_attention_mma(qc[:, :, :r], qc[:, :, r:], mixed, cache.k, ctx.positions, ctx.q_start, table,
-                                     ctx.n_requests, ctx.host.max_q_len, self.scale, self.window)
+            ops.latent_attention_mma(qc[:, :, :r], qc[:, :, r:], mixed, cache.k, ctx.positions, ctx.q_start, ctx.req_of_token,
+                                     table, ctx.n_requests, ctx.host.max_q_len, self.scale, self.window,
+                                     n_splits=self._splits(ctx))
         else:
             mixed = ops.latent_attention_exact(qc, cache.k, ctx.positions, ctx.req_of_token, table, r, self.scale, self.window)
         ops.head_project(mixed, self.uv, y.unflatten(1, (nh, e)), gate=gate, req_of_token=ctx.req_of_token)
