@@ -122,10 +122,24 @@ __global__ void route_kernel(const T* __restrict__ x, long x_stride, const float
   }
   for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_f32<T>(x[(size_t)n * x_stride + k]);
   __syncthreads();
+  const bool vec = (K & 3) == 0 && ((uintptr_t)w & 15) == 0;      // four k a lane and load: another fixed order of the same sum
   for (int e = warp; e < E; e += warps) {
     const float* wr = w + (size_t)e * K;
     float acc = 0.f;
-    for (int k = lane; k < K; k += 32) acc = __fmaf_rn(wr[k], xs[k], acc);
+    if (vec) {
+#pragma unroll 4
+      for (int k = 4 * lane; k < K; k += 128) {
+        const float4 wv = *reinterpret_cast<const float4*>(wr + k);
+        const float4 xv = *reinterpret_cast<const float4*>(xs + k);
+        acc = __fmaf_rn(wv.x, xv.x, acc);
+        acc = __fmaf_rn(wv.y, xv.y, acc);
+        acc = __fmaf_rn(wv.z, xv.z, acc);
+        acc = __fmaf_rn(wv.w, xv.w, acc);
+      }
+    } else {
+#pragma unroll 4
+      for (int k = lane; k < K; k += 32) acc = __fmaf_rn(wr[k], xs[k], acc);
+    }
     acc = warp_sum(acc);
     if (lane == 0) z[e] = acc;
   }
@@ -249,22 +263,27 @@ __global__ void grouped_gemm_simt_kernel(const GroupedArgs g) {
   }
 }
 
-// bfloat16 on mma.sync.m16n8k16: BM x 64 tile, 4 warps, K in steps of 32 through a two-stage cp.async ring.
-// BM = 32: warps side by side along the columns (16 each); BM = 128: warps stacked along the rows (32 each).
-// Needs K % 8 == 0 and 16-byte aligned rows of A and W.
+// bfloat16 on mma.sync.m16n8k16 with ldmatrix-fed fragments: a BM x BN tile per block, K in steps of 64 through a
+// ring of cp.async stages.  Two shapes: 128 x 128 with 8 warps (64 x 32 each) and 3 stages for steps in which an
+// expert gets many tokens, and 32 x 64 with 4 warps (32 x 16 each) and 5 stages for steps of few tokens, where the
+// weights stream through once and what counts is how many bytes are in flight.  Needs K % 8 == 0 and 16-byte
+// aligned rows of A and W.
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
   const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
   const int bytes = valid ? 16 : 0;
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(bytes) : "memory");
 }
 
-template <int BM>
-__global__ void __launch_bounds__(128) grouped_gemm_mma_kernel(const GroupedArgs g) {
-  constexpr int BN = 64, BK = 32, LD = BK + 8;          // rows of 80 bytes: fragment loads hit 32 distinct banks
-  constexpr int WARPS_M = BM / 32, WARPS_N = 4 / WARPS_M, WN = BN / WARPS_N, NT = WN / 8;
-  __shared__ __align__(16) __nv_bfloat16 As[2][BM][LD];
-  __shared__ __align__(16) __nv_bfloat16 Bs[2][BN][LD];
-  __shared__ int rows[BM];
+template <int BM, int BN, int BK, int WARPS_M, int WARPS_N, int STAGES>
+__global__ void __launch_bounds__(32 * WARPS_M * WARPS_N) grouped_gemm_mma_kernel(const GroupedArgs g) {
+  constexpr int LD = BK + 8, CH = BK / 8;               // rows of 80 or 144 bytes: ldmatrix reads 8 distinct 16-byte lanes
+  constexpr int THREADS = 32 * WARPS_M * WARPS_N;
+  constexpr int WTM = BM / WARPS_M, WTN = BN / WARPS_N, MT = WTM / 16, NT = WTN / 8;
+  static_assert(WTM % 16 == 0 && WTN % 16 == 0, "warp tiles are made of 16 x 16 pieces");
+  extern __shared__ __align__(16) unsigned char gg_smem[];
+  __nv_bfloat16* As = reinterpret_cast<__nv_bfloat16*>(gg_smem);                 // [STAGES][BM][LD]
+  __nv_bfloat16* Bs = As + (size_t)STAGES * BM * LD;                            // [STAGES][BN][LD]
+  int* rows = reinterpret_cast<int*>(Bs + (size_t)STAGES * BN * LD);            // [BM]
   pdl_launch_dependents();
   pdl_wait();
   if ((int)blockIdx.x >= *g.n_tiles) return;
@@ -273,80 +292,103 @@ __global__ void __launch_bounds__(128) grouped_gemm_mma_kernel(const GroupedArgs
   const int n0 = blockIdx.y * BN;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int wm = warp / WARPS_N, wn = warp % WARPS_N;
-  for (int i = tid; i < BM; i += 128) rows[i] = i < m_rows ? (g.perm ? g.perm[slot0 + i] / g.top : slot0 + i) : -1;
+  for (int i = tid; i < BM; i += THREADS) rows[i] = i < m_rows ? (g.perm ? g.perm[slot0 + i] / g.top : slot0 + i) : -1;
   __syncthreads();
   const __nv_bfloat16* A = reinterpret_cast<const __nv_bfloat16*>(g.a);
   const __nv_bfloat16* W = reinterpret_cast<const __nv_bfloat16*>(g.w) + (size_t)e * g.n_out * g.K;
+  const int steps = (g.K + BK - 1) / BK;
 
-  auto load = [&](int stage, int k0) {
-    for (int i = tid; i < BM * 4; i += 128) {
-      const int r = i >> 2, ch = i & 3;
-      const bool ok = rows[r] >= 0 && k0 + ch * 8 < g.K;
-      cp_async16(&As[stage][r][ch * 8], ok ? A + (size_t)rows[r] * g.a_stride + k0 + ch * 8 : A, ok);
+  auto load = [&](int step) {
+    if (step < steps) {
+      const int stage = step % STAGES, k0 = step * BK;
+      __nv_bfloat16* as = As + (size_t)stage * BM * LD;
+      __nv_bfloat16* bs = Bs + (size_t)stage * BN * LD;
+      for (int i = tid; i < BM * CH; i += THREADS) {
+        const int r = i / CH, ch = i % CH;
+        const bool ok = rows[r] >= 0 && k0 + ch * 8 < g.K;
+        cp_async16(as + r * LD + ch * 8, ok ? A + (size_t)rows[r] * g.a_stride + k0 + ch * 8 : A, ok);
+      }
+      for (int i = tid; i < BN * CH; i += THREADS) {
+        const int r = i / CH, ch = i % CH;
+        const bool ok = n0 + r < g.n_out && k0 + ch * 8 < g.K;
+        cp_async16(bs + r * LD + ch * 8, ok ? W + (size_t)(n0 + r) * g.K + k0 + ch * 8 : W, ok);
+      }
     }
-    for (int i = tid; i < BN * 4; i += 128) {
-      const int r = i >> 2, ch = i & 3;
-      const bool ok = n0 + r < g.n_out && k0 + ch * 8 < g.K;
-      cp_async16(&Bs[stage][r][ch * 8], ok ? W + (size_t)(n0 + r) * g.K + k0 + ch * 8 : W, ok);
-    }
-    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.commit_group;" ::: "memory");   // a group per step, empty past the end: the count below holds
   };
 
-  float acc[2][NT][4] = {};
-  const int steps = (g.K + BK - 1) / BK;
-  load(0, 0);
-  for (int s = 0; s < steps; ++s) {
-    if (s + 1 < steps) {
-      load((s + 1) & 1, (s + 1) * BK);
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-    }
-    __syncthreads();
-    const int st = s & 1;
-    const int gq = lane >> 2, tq = lane & 3;
+  float acc[MT][NT][4] = {};
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; ++st) load(st);
+  for (int step = 0; step < steps; ++step) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
+    __syncthreads();                                       // step's tile is in place; everyone is done with step - 1
+    load(step + STAGES - 1);                               // into the stage that step - 1 used
+    const __nv_bfloat16* as = As + (size_t)(step % STAGES) * BM * LD;
+    const __nv_bfloat16* bs = Bs + (size_t)(step % STAGES) * BN * LD;
 #pragma unroll
     for (int kk = 0; kk < BK; kk += 16) {
-      uint32_t af[2][4];
+      uint32_t af[MT][4], bf[NT][2];
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt) {
-        const int r = wm * 32 + mt * 16 + gq;
-        af[mt][0] = *reinterpret_cast<const uint32_t*>(&As[st][r][kk + 2 * tq]);
-        af[mt][1] = *reinterpret_cast<const uint32_t*>(&As[st][r + 8][kk + 2 * tq]);
-        af[mt][2] = *reinterpret_cast<const uint32_t*>(&As[st][r][kk + 2 * tq + 8]);
-        af[mt][3] = *reinterpret_cast<const uint32_t*>(&As[st][r + 8][kk + 2 * tq + 8]);
+      for (int mt = 0; mt < MT; ++mt) {
+        const unsigned addr = (unsigned)__cvta_generic_to_shared(as + (wm * WTM + mt * 16 + (lane & 15)) * LD + kk + (lane >> 4) * 8);
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(af[mt][0]), "=r"(af[mt][1]), "=r"(af[mt][2]), "=r"(af[mt][3]) : "r"(addr));
       }
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        const int c = wn * WN + nt * 8 + gq;
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&Bs[st][c][kk + 2 * tq]);
-        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&Bs[st][c][kk + 2 * tq + 8]);
+      for (int np = 0; np < NT / 2; ++np) {
+        const unsigned addr = (unsigned)__cvta_generic_to_shared(
+            bs + (wn * WTN + np * 16 + (lane & 7) + ((lane >> 4) << 3)) * LD + kk + ((lane >> 3) & 1) * 8);
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(bf[2 * np][0]), "=r"(bf[2 * np][1]), "=r"(bf[2 * np + 1][0]), "=r"(bf[2 * np + 1][1]) : "r"(addr));
+      }
 #pragma unroll
-        for (int mt = 0; mt < 2; ++mt)
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
           asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                        : "+f"(acc[mt][nt][0]), "+f"(acc[mt][nt][1]), "+f"(acc[mt][nt][2]), "+f"(acc[mt][nt][3])
-                       : "r"(af[mt][0]), "r"(af[mt][1]), "r"(af[mt][2]), "r"(af[mt][3]), "r"(b0), "r"(b1));
-      }
+                       : "r"(af[mt][0]), "r"(af[mt][1]), "r"(af[mt][2]), "r"(af[mt][3]), "r"(bf[nt][0]), "r"(bf[nt][1]));
     }
-    __syncthreads();
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
   __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(g.c);
   const int gq = lane >> 2, tq = lane & 3;
+  const bool pairs = (g.c_stride & 1) == 0 && ((uintptr_t)C & 3) == 0;
 #pragma unroll
-  for (int mt = 0; mt < 2; ++mt)
+  for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
-      const int r = wm * 32 + mt * 16 + gq + half * 8;
+      const int r = wm * WTM + mt * 16 + gq + half * 8;
       if (r >= m_rows) continue;
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        const int c = n0 + wn * WN + nt * 8 + 2 * tq;
+        const int c = n0 + wn * WTN + nt * 8 + 2 * tq;
         __nv_bfloat16* dst = C + (size_t)(slot0 + r) * g.c_stride + c;
         const float v0 = apply_act(acc[mt][nt][half * 2], g.act), v1 = apply_act(acc[mt][nt][half * 2 + 1], g.act);
-        if (c < g.n_out) dst[0] = __float2bfloat16_rn(v0);
-        if (c + 1 < g.n_out) dst[1] = __float2bfloat16_rn(v1);
+        if (pairs && c + 1 < g.n_out) {
+          *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(v0, v1);
+        } else {
+          if (c < g.n_out) dst[0] = __float2bfloat16_rn(v0);
+          if (c + 1 < g.n_out) dst[1] = __float2bfloat16_rn(v1);
+        }
       }
     }
+}
+
+template <int BM, int BN, int BK, int WARPS_M, int WARPS_N, int STAGES>
+int launch_grouped_mma(const GroupedArgs& g, int max_tiles, cudaStream_t stream) {
+  const size_t smem = (size_t)STAGES * (BM + BN) * (BK + 8) * 2 + BM * 4;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(grouped_gemm_mma_kernel<BM, BN, BK, WARPS_M, WARPS_N, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+      return YALIS_ERR_LAUNCH;
+    configured = true;
+  }
+  const dim3 grid(max_tiles, (g.n_out + BN - 1) / BN);
+  if (grid.y > 65535) return YALIS_ERR_SHAPE;
+  return yalis_launch(grouped_gemm_mma_kernel<BM, BN, BK, WARPS_M, WARPS_N, STAGES>, grid, dim3(32 * WARPS_M * WARPS_N), smem, stream, g);
 }
 
 // out[n, :] = sum_j weights[n, j] * y[inv[n * top + j], :] + shared[n, :]
@@ -465,8 +507,8 @@ YALIS_API int yalis_grouped_gemm(const void* a, long a_stride, const int32_t* pe
   if (tensor_cores) {
     if (dtype != YALIS_BF16) return YALIS_ERR_DTYPE;
     if (K % 8 || a_stride % 8 || ((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return YALIS_ERR_ALIGN;
-    if (bm == 32) return yalis_launch(grouped_gemm_mma_kernel<32>, grid, dim3(128), 0, stream, g);
-    if (bm == 128) return yalis_launch(grouped_gemm_mma_kernel<128>, grid, dim3(128), 0, stream, g);
+    if (bm == 32) return launch_grouped_mma<32, 64, 64, 1, 4, 5>(g, max_tiles, stream);
+    if (bm == 128) return launch_grouped_mma<128, 128, 64, 2, 4, 3>(g, max_tiles, stream);
     return YALIS_ERR_SHAPE;
   }
   if (bm != 32) return YALIS_ERR_SHAPE;

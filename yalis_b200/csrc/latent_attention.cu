@@ -307,18 +307,19 @@ __global__ void __launch_bounds__(128 * WR) latent_attention_mma_kernel(const La
   const int chunks = W / 8;
   const int step = a.n_splits, tile_first = blockIdx.z;
 
-  auto load = [&](int tile, int buf) {
-    // TPR threads per row: one page lookup each, then 16-byte pieces in turn
+  // TPR threads per row of a tile: each looks its row's page up one tile before the tile is asked for (the lookup is a
+  // trip to the L2 that would otherwise sit between a tile's arrival and its use), then copies 16-byte pieces in turn
+  auto page_of = [&](int tile) {
+    const int j = lo + tile * kKeyTile + tid / TPR;
+    if (tile >= n_tiles || j > pos_last) return -1;
+    const int pi = j / a.page_size;
+    return pi < a.table_width ? bt[pi] : -1;
+  };
+  auto load = [&](int tile, int buf, int page) {
     __nv_bfloat16* dst = Ks + (size_t)buf * kKeyTile * LD;
     const int r = tid / TPR, j = lo + tile * kKeyTile + r;
-    const __nv_bfloat16* src = a.pool;
-    bool ok = j <= pos_last;
-    if (ok) {
-      const int pi = j / a.page_size;
-      const int page = pi < a.table_width ? bt[pi] : -1;
-      ok = page >= 0 && page < a.num_pages;
-      if (ok) src = a.pool + ((size_t)page * a.page_size + (j - pi * a.page_size)) * W;
-    }
+    const bool ok = page >= 0 && page < a.num_pages;
+    const __nv_bfloat16* src = ok ? a.pool + ((size_t)page * a.page_size + (j % a.page_size)) * W : a.pool;
     for (int ch = tid % TPR; ch < chunks; ch += TPR) cp_async_16(dst + r * LD + ch * 8, ok ? src + ch * 8 : a.pool, ok);
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -333,15 +334,16 @@ __global__ void __launch_bounds__(128 * WR) latent_attention_mma_kernel(const La
       l_run[mt][hf] = 0.f;
     }
 
-  if (tile_first < n_tiles) load(tile_first, 0);
-  int buf = 0;
+  if (tile_first < n_tiles) load(tile_first, 0, page_of(tile_first));
+  int buf = 0, page_next = page_of(tile_first + step);
   for (int tile = tile_first; tile < n_tiles; tile += step, buf ^= 1) {
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();                                // this tile is in place; everyone is done with the one before
-    if (tile + step < n_tiles) load(tile + step, buf ^ 1);
+    if (tile + step < n_tiles) load(tile + step, buf ^ 1, page_next);
+    page_next = page_of(tile + 2 * step);
     const __nv_bfloat16* Kt = Ks + (size_t)buf * kKeyTile * LD;
     // scores of this warp's 16 rows for its group's 32 queries
-    float s[2][2][4] = {};
+    float s[2][2][4] = {}, s2[2][2][4] = {};           // even and odd steps of K apart: twice the MMAs in flight
     for (int k0 = 0; k0 < W; k0 += 16) {
       uint32_t af[2][4];
 #pragma unroll
@@ -357,9 +359,18 @@ __global__ void __launch_bounds__(128 * WR) latent_attention_mma_kernel(const La
         const __nv_bfloat16* kp = Kt + (wc * 16 + nt * 8 + gq) * LD + k0 + 2 * tq;
         const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kp), b1 = *reinterpret_cast<const uint32_t*>(kp + 8);
 #pragma unroll
-        for (int mt = 0; mt < 2; ++mt) mma_bf16(s[mt][nt], af[mt], b0, b1);
+        for (int mt = 0; mt < 2; ++mt) {
+          if (k0 & 16) mma_bf16(s2[mt][nt], af[mt], b0, b1);
+          else mma_bf16(s[mt][nt], af[mt], b0, b1);
+        }
       }
     }
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[mt][nt][e] += s2[mt][nt][e];
     // mask, scale, row maxima of this warp's keys
     const int key0 = lo + tile * kKeyTile + wc * 16;
 #pragma unroll
@@ -500,7 +511,8 @@ __global__ void __launch_bounds__(128 * WR) latent_attention_mma_kernel(const La
     }
 }
 
-// out = sum_z o_z exp(m_z - M) / sum_z l_z exp(m_z - M) in the order of z.  One warp per (token, head).
+// out = sum_z o_z exp(m_z - M) / sum_z l_z exp(m_z - M) in the order of z (at most 32 shares).  One warp per
+// (token, head): lane z weighs share z, then every column adds its shares in the order of z.
 __global__ void latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int n_splits,
                                     int n_tokens, int heads, int r, const int32_t* __restrict__ req_of_token, void* out,
                                     int out_bf16, long o_n, long o_h) {
@@ -510,19 +522,21 @@ __global__ void latent_merge_kernel(const float* __restrict__ part_o, const floa
   if (row >= n_tokens * heads) return;
   const int tok = row / heads, h = row - tok * heads;
   if (req_of_token[tok] < 0) return;
-  float M = -INFINITY;
-  for (int z = 0; z < n_splits; ++z) M = fmaxf(M, part_ml[((size_t)z * n_tokens * heads + row) * 2]);
-  float l = 0.f;
-  for (int z = 0; z < n_splits; ++z) {
-    const float m = part_ml[((size_t)z * n_tokens * heads + row) * 2];
-    if (m != -INFINITY) l += part_ml[((size_t)z * n_tokens * heads + row) * 2 + 1] * expf(m - M);
-  }
+  const size_t rows = (size_t)n_tokens * heads;
+  const float m = lane < n_splits ? part_ml[((size_t)lane * rows + row) * 2] : -INFINITY;
+  const float lz = lane < n_splits ? part_ml[((size_t)lane * rows + row) * 2 + 1] : 0.f;
+  const float M = warp_max(m);
+  const float wz = m == -INFINITY ? 0.f : expf(m - M);
+  const float l = warp_sum(lz * wz);
   const float inv = l > 0.f ? 1.0f / l : 0.f;
   for (int c = lane; c < r; c += 32) {
     float acc = 0.f;
+#pragma unroll 8
     for (int z = 0; z < n_splits; ++z) {
-      const float m = part_ml[((size_t)z * n_tokens * heads + row) * 2];
-      if (m != -INFINITY) acc += part_o[((size_t)z * n_tokens * heads + row) * r + c] * expf(m - M);
+      // loaded whether it counts or not (a share without rows holds no numbers), so that the loads go out together
+      const float v = part_o[((size_t)z * rows + row) * r + c];
+      const float w = __shfl_sync(0xffffffffu, wz, z);
+      acc = __fmaf_rn(w > 0.f ? v : 0.f, w, acc);
     }
     const size_t at = (size_t)tok * o_n + (size_t)h * o_h + c;
     if (out_bf16) reinterpret_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(acc * inv);
@@ -648,7 +662,7 @@ YALIS_API int yalis_latent_attention_mma(const void* q_lat, int q_lat_bf16, long
                                          int n_requests, int n_tokens, int max_q_len, int heads, int r, int p, float scale,
                                          int window, int n_splits, float* part_o, float* part_ml, cudaStream_t stream) {
   if (n_requests <= 0 || max_q_len <= 0) return YALIS_OK;
-  if (!yalis_latent_attention_mma_supports(r, p) || heads <= 0 || n_requests > 65535 || n_splits < 1 || n_splits > 65535)
+  if (!yalis_latent_attention_mma_supports(r, p) || heads <= 0 || n_requests > 65535 || n_splits < 1 || n_splits > 32)
     return YALIS_ERR_SHAPE;
   if (n_splits > 1 && (part_o == nullptr || part_ml == nullptr)) return YALIS_ERR_SHAPE;
   if ((uintptr_t)pool & 15) return YALIS_ERR_ALIGN;

@@ -97,9 +97,10 @@ class LatentAttention(Mixer, Projected):
     def cache_request(self) -> PagedKV:
         return PagedKV(1, self.r + self.p, self.cache_window, v_head_dim=0)
 
-    # From this many tokens on a bfloat16 step runs the two per-head maps as batched library products (the tensor
-    # cores); below, on the engine's own kernel, which streams each head's matrix once per token.
-    BATCHED_FROM = 65
+    # A bfloat16 step whose shapes the tensor-core attention takes runs the two per-head maps as batched library
+    # products (measured at 8 tokens, 16 heads of 128 x 256: 41 us on the engine's own kernel, which stays the
+    # float32 path's and that of other shapes).
+    BATCHED_FROM = 1
 
     def _tensor_core_form(self, dtype: torch.dtype) -> bool:
         return dtype == torch.bfloat16 and ops.mma_supports(self.r, self.p)
@@ -141,7 +142,7 @@ class LatentAttention(Mixer, Projected):
             mixed = torch.empty((nh, n, r), dtype=z.dtype, device=z.device)
             ops.latent_attention_mma(q_lat.transpose(0, 1), qc[:, :, r:], mixed.transpose(0, 1), cache.k, ctx.positions,
                                      ctx.q_start, ctx.req_of_token, table, ctx.n_requests, ctx.host.max_q_len, self.scale,
-                                     self.window)
+                                     self.window, n_splits=self._splits(ctx))
             o = torch.bmm(mixed, self.uv_t)                                               # [H, N, e]
             if gate is not None:
                 ops.sigmoid_gate(o.transpose(0, 1), gate, y)
