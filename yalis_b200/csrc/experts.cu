@@ -102,49 +102,70 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int E, int t
 }
 
 // The router whole: logits = W x in float32 (x may be bfloat16; sums per lane in k order, then a fixed butterfly) and
-// the choice, one block per token.  The token's row waits in shared memory as float32; warps share out the experts.
-template <typename T>
+// the choice.  A block takes TOK tokens: their rows wait in shared memory in their own dtype, the warps share out
+// the experts, and a row of the router read once serves all TOK tokens (each token's sum has the same order whatever
+// TOK is); then warp t chooses for token t.
+template <typename T, int TOK>
 __global__ void route_kernel(const T* __restrict__ x, long x_stride, const float* __restrict__ w, int E, int K, int top,
                              float eps, const int32_t* __restrict__ req_of_token, int32_t* __restrict__ ids,
-                             float* __restrict__ weights) {
-  extern __shared__ float route_smem[];   // [K] the row, then [E] the logits
-  float* xs = route_smem;
-  float* z = route_smem + K;
+                             float* __restrict__ weights, int n_tokens) {
+  extern __shared__ __align__(16) unsigned char route_smem[];   // [TOK][K] rows (T), then [TOK][E] logits (float)
+  T* xs = reinterpret_cast<T*>(route_smem);
+  float* z = reinterpret_cast<float*>(route_smem + (((size_t)TOK * K * sizeof(T) + 15) & ~(size_t)15));
   pdl_launch_dependents();
   pdl_wait();
-  const int n = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-  if (req_of_token && req_of_token[n] < 0) {
-    for (int j = threadIdx.x; j < top; j += blockDim.x) {
-      ids[(size_t)n * top + j] = -1;
-      weights[(size_t)n * top + j] = 0.f;
-    }
-    return;
+  const int n0 = blockIdx.x * TOK, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int here = min(TOK, n_tokens - n0);
+  for (int i = threadIdx.x; i < TOK * K; i += blockDim.x) {
+    const int t = i / K, k = i - t * K;
+    xs[i] = t < here ? x[(size_t)(n0 + t) * x_stride + k] : from_f32<T>(0.f);
   }
-  for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_f32<T>(x[(size_t)n * x_stride + k]);
   __syncthreads();
-  const bool vec = (K & 3) == 0 && ((uintptr_t)w & 15) == 0;      // four k a lane and load: another fixed order of the same sum
   for (int e = warp; e < E; e += warps) {
     const float* wr = w + (size_t)e * K;
-    float acc = 0.f;
-    if (vec) {
+    float acc[TOK];
+#pragma unroll
+    for (int t = 0; t < TOK; ++t) acc[t] = 0.f;
 #pragma unroll 4
-      for (int k = 4 * lane; k < K; k += 128) {
-        const float4 wv = *reinterpret_cast<const float4*>(wr + k);
-        const float4 xv = *reinterpret_cast<const float4*>(xs + k);
-        acc = __fmaf_rn(wv.x, xv.x, acc);
-        acc = __fmaf_rn(wv.y, xv.y, acc);
-        acc = __fmaf_rn(wv.z, xv.z, acc);
-        acc = __fmaf_rn(wv.w, xv.w, acc);
-      }
-    } else {
-#pragma unroll 4
-      for (int k = lane; k < K; k += 32) acc = __fmaf_rn(wr[k], xs[k], acc);
+    for (int k = lane; k < K; k += 32) {
+      const float wv = wr[k];
+#pragma unroll
+      for (int t = 0; t < TOK; ++t) acc[t] = __fmaf_rn(wv, to_f32<T>(xs[t * K + k]), acc[t]);
     }
-    acc = warp_sum(acc);
-    if (lane == 0) z[e] = acc;
+#pragma unroll
+    for (int t = 0; t < TOK; ++t) {
+      const float v = warp_sum(acc[t]);
+      if (lane == 0) z[t * E + e] = v;
+    }
   }
   __syncthreads();
-  if (warp == 0) choose_experts([&](int e) { return z[e]; }, E, top, eps, lane, ids + (size_t)n * top, weights + (size_t)n * top);
+  for (int t = warp; t < here; t += warps) {
+    const int n = n0 + t;
+    if (req_of_token && req_of_token[n] < 0) {
+      for (int j = lane; j < top; j += 32) {
+        ids[(size_t)n * top + j] = -1;
+        weights[(size_t)n * top + j] = 0.f;
+      }
+      continue;
+    }
+    const float* zt = z + t * E;
+    choose_experts([&](int e) { return zt[e]; }, E, top, eps, lane, ids + (size_t)n * top, weights + (size_t)n * top);
+  }
+}
+
+template <typename T, int TOK>
+int launch_route(const void* x, long x_stride, const float* w, int n_tokens, int E, int K, int top, float eps,
+                 const int32_t* req_of_token, int32_t* ids, float* weights, cudaStream_t stream) {
+  const size_t smem = (((size_t)TOK * K * sizeof(T) + 15) & ~(size_t)15) + (size_t)TOK * E * sizeof(float);
+  if (smem > 200 * 1024) return YALIS_ERR_SHAPE;
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    if (cudaFuncSetAttribute(route_kernel<T, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return YALIS_ERR_LAUNCH;
+    configured = smem;
+  }
+  return yalis_launch(route_kernel<T, TOK>, dim3((n_tokens + TOK - 1) / TOK), dim3(256), smem, stream, (const T*)x, x_stride, w, E, K,
+                      top, eps, req_of_token, ids, weights, n_tokens);
 }
 
 // One block.  entries = n_tokens * top.  tiles: (expert, first slot) per row tile of `bm` slots, ended by n_tiles.
@@ -265,8 +286,8 @@ __global__ void grouped_gemm_simt_kernel(const GroupedArgs g) {
 
 // bfloat16 on mma.sync.m16n8k16 with ldmatrix-fed fragments: a BM x BN tile per block, K in steps of 64 through a
 // ring of cp.async stages.  Two shapes: 128 x 128 with 8 warps (64 x 32 each) and 3 stages for steps in which an
-// expert gets many tokens, and 32 x 64 with 4 warps (32 x 16 each) and 5 stages for steps of few tokens, where the
-// weights stream through once and what counts is how many bytes are in flight.  Needs K % 8 == 0 and 16-byte
+// expert gets many tokens, and 32 x 64 (5 stages) or 16 x 64 (8 stages) with 4 warps for steps of few tokens, where
+// the weights stream through once and what counts is how many bytes are in flight (16 rows: 112 KB an SM).  Needs K % 8 == 0 and 16-byte
 // aligned rows of A and W.
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
   const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -460,27 +481,17 @@ YALIS_API int yalis_route_topk(const float* logits, int n_tokens, int E, int top
                       eps, req_of_token, ids, weights, n_tokens);
 }
 
-// The router and the choice in one launch.  x: [n_tokens, K] float32 or bfloat16; w: float32 [E, K].
+// The router and the choice in one launch.  x: [n_tokens, K] float32 or bfloat16; w: float32 [E, K].  Steps of many
+// tokens take eight to a block where their rows fit shared memory.
 YALIS_API int yalis_route(const void* x, int x_dtype, long x_stride, const float* w, int n_tokens, int E, int K, int top, float eps,
                           const int32_t* req_of_token, int32_t* ids, float* weights, cudaStream_t stream) {
   if (n_tokens <= 0) return YALIS_OK;
-  if (E <= 0 || E > kMaxExperts || top <= 0 || top > kMaxTop || top > E || K <= 0 || (size_t)(K + E) * 4 > 200 * 1024)
-    return YALIS_ERR_SHAPE;
-  const size_t smem = (size_t)(K + E) * sizeof(float);
-  if (smem > 48 * 1024) {
-    static size_t configured[2] = {0, 0};
-    const int which = x_dtype == YALIS_BF16 ? 1 : 0;
-    if (smem > configured[which]) {
-      const cudaError_t err = which ? cudaFuncSetAttribute(route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                                    : cudaFuncSetAttribute(route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (err != cudaSuccess) return YALIS_ERR_LAUNCH;
-      configured[which] = smem;
-    }
-  }
-  const int threads = E >= 8 ? 256 : 128;
+  if (E <= 0 || E > kMaxExperts || top <= 0 || top > kMaxTop || top > E || K <= 0) return YALIS_ERR_SHAPE;
+  const size_t elt = x_dtype == YALIS_BF16 ? 2 : 4;
+  const bool many = n_tokens >= 64 && 8 * ((size_t)K * elt + (size_t)E * 4) + 16 <= 96 * 1024;
   YALIS_DISPATCH_DTYPE(x_dtype, T,
-                       return yalis_launch(route_kernel<T>, dim3(n_tokens), dim3(threads), smem, stream, (const T*)x, x_stride, w, E,
-                                           K, top, eps, req_of_token, ids, weights));
+                       return many ? launch_route<T, 8>(x, x_stride, w, n_tokens, E, K, top, eps, req_of_token, ids, weights, stream)
+                                   : launch_route<T, 1>(x, x_stride, w, n_tokens, E, K, top, eps, req_of_token, ids, weights, stream));
   return YALIS_OK;
 }
 
@@ -493,7 +504,7 @@ YALIS_API int yalis_expert_plan(const int32_t* ids, int entries, int E, int bm, 
                       tile_expert, tile_slot, n_tiles);
 }
 
-// bm: the row tile the plan was made for (32 or 128 for the tensor-core form, 32 for the other).
+// bm: the row tile the plan was made for (16, 32 or 128 for the tensor-core form, 32 for the other).
 YALIS_API int yalis_grouped_gemm(const void* a, long a_stride, const int32_t* perm, int top, const void* w, void* c,
                                  long c_stride, int dtype, const int32_t* offsets, const int32_t* tile_expert,
                                  const int32_t* tile_slot, const int32_t* n_tiles, int max_tiles, int n_out, int K, int act,
@@ -507,6 +518,7 @@ YALIS_API int yalis_grouped_gemm(const void* a, long a_stride, const int32_t* pe
   if (tensor_cores) {
     if (dtype != YALIS_BF16) return YALIS_ERR_DTYPE;
     if (K % 8 || a_stride % 8 || ((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return YALIS_ERR_ALIGN;
+    if (bm == 16) return launch_grouped_mma<16, 64, 64, 1, 4, 8>(g, max_tiles, stream);
     if (bm == 32) return launch_grouped_mma<32, 64, 64, 1, 4, 5>(g, max_tiles, stream);
     if (bm == 128) return launch_grouped_mma<128, 128, 64, 2, 4, 3>(g, max_tiles, stream);
     return YALIS_ERR_SHAPE;

@@ -102,7 +102,7 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, plan: ExpertPlan, *, gather_t
     if out is None:
         out = torch.empty((plan.entries, n_out), dtype=a.dtype, device=a.device)
     need(out.shape == (plan.entries, n_out) and out.dtype == a.dtype and out.stride(1) == 1, name, "bad out tensor")
-    tc = tensor_core_form(a, w) and plan.bm in (32, 128)
+    tc = tensor_core_form(a, w) and plan.bm in (16, 32, 128)
     need(tc or plan.bm == 32, name, "the plan's row tile does not fit the kernel that takes these operands")
     check(lib().yalis_grouped_gemm(ptr(a), i64(a.stride(0)), ptr(plan.perm if gather_top else None), i32(gather_top or 1),
                                    ptr(w), ptr(out), i64(out.stride(0)), i32(dtype_code(a.dtype)), ptr(plan.offsets),

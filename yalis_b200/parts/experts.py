@@ -76,11 +76,15 @@ class RoutedExperts(FeedForward):
         return unused * (self.w_up[0].numel() + self.w_down[0].numel()) * self.w_up.element_size()
 
     def row_tile(self, x: torch.Tensor) -> int:
-        """Rows of a tile of the experts' products: 128 where the tensor-core form runs and an expert gets that many
-        tokens on average, else 32."""
+        """Rows of a tile of the experts' products.  Where the tensor-core form runs: 128 when an expert gets about that
+        many tokens on average, 16 when it gets at most 8 (a decode step: small tiles leave shared memory to a deeper
+        ring of weight tiles), else 32.  The other form has tiles of 32."""
         tc = (x.dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.inner % 8 == 0 and x.stride(0) % 8 == 0
               and x.data_ptr() % 16 == 0)
-        return 128 if tc and x.shape[0] * self.top >= 96 * self.n_experts else 32
+        if not tc:
+            return 32
+        entries = x.shape[0] * self.top
+        return 128 if entries >= 96 * self.n_experts else (16 if entries <= 8 * self.n_experts else 32)
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         ids, weights = ops.route(x, self.router, self.top, self.eps, ctx.req_of_token if ctx is not None else None)
