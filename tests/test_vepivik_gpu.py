@@ -333,6 +333,39 @@ def test_routed_experts_against_the_plain_mixture(dtype, n, hidden, experts, top
         assert float(err.median()) < 2e-2 and float((err > 4e-2).float().mean()) <= 0.03, float(err.max())
 
 
+@pytest.mark.parametrize("n, hidden, experts, top, inner, shared", [(8, 128, 16, 2, 64, 32), (70, 64, 4, 2, 72, None), (600, 128, 4, 2, 200, 64),
+                                                                  (2500, 256, 8, 2, 136, None), (40, 64, 2, 2, 8, None)])
+def test_the_two_tensor_core_forms_of_the_experts_products_agree(n, hidden, experts, top, inner, shared, monkeypatch):
+    """tcgen05 with TMA-streamed operands (every row tile from 16 to 256, experts with more rows than a tile, inner sizes
+    that end inside a 128-row box of weights) against the mma.sync form and the plain mixture; no wait runs out."""
+    from yalis_b200.config.spec import PartSpec
+    from yalis_b200.ops import _lib
+    from yalis_b200.parts.base import make_part
+    t = ff_tensors(hidden, experts, inner, shared, seed=n, dtype=torch.bfloat16)
+    part = make_part("feed_forward", PartSpec("routed_experts", {"hidden_size": hidden, "experts": experts, "top": top,
+                                                                 "expert_size": inner, "activation": "relu2", "shared_size": shared}))
+    local = {"router": t["router"].float().to(DEV)}
+    for e in range(experts):
+        local[f"expert_{e}_up"], local[f"expert_{e}_down"] = t[f"e{e}.up"].to(DEV), t[f"e{e}.down"].to(DEV)
+    if shared:
+        local["shared_up"], local["shared_down"] = t["shared.up"].to(DEV), t["shared.down"].to(DEV)
+    part.load(local)
+    x = torch.randn(n, hidden, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).to(DEV)
+    monkeypatch.delenv("YALIS_B200_NO_GROUPED_TCGEN05", raising=False)
+    streamed = part.forward(x, None)
+    assert torch.equal(streamed, part.forward(x, None))
+    monkeypatch.setenv("YALIS_B200_NO_GROUPED_TCGEN05", "1")
+    other = part.forward(x, None)
+    assert int(_lib.error_word(x.device).item()) == 0
+    # the same routing, float32 sums of the same bfloat16 products in another order, one rounding: a few last bits apart
+    diff = (streamed.float() - other.float()).abs().max(dim=1).values / other.float().abs().max()
+    assert float(diff.max()) < 2e-2 and float((diff > 4e-3).float().mean()) < 0.02, float(diff.max())
+    mlp = {"router": {"experts": experts, "top": top}, "shared": {"ff": shared} if shared else None}
+    want = plain.mixture_of_experts(x.double().cpu(), {"p." + k: v.double() for k, v in t.items()}, "p.", mlp)
+    err = (streamed.double().cpu() - want).abs().max(dim=1).values / want.abs().max()
+    assert float(err.median()) < 2e-2 and float((err > 4e-2).float().mean()) <= 0.03, float(err.max())
+
+
 def test_the_order_of_tokens_inside_an_expert_leaves_no_trace():
     """The grouping uses atomics; the results must have the same bits every time, and a token's result must not depend
     on what else is in the batch."""

@@ -247,6 +247,18 @@ __global__ void expert_plan_kernel(const int32_t* __restrict__ ids, int entries,
   }
 }
 
+// xg[slot, :] = x[perm[slot] / top, :] for the slots in use (16-byte pieces): the rows of every expert side by side,
+// as a product that reads its rows as one box needs them.
+__global__ void gather_rows_kernel(const uint4* __restrict__ x, long x_stride16, const int32_t* __restrict__ perm, int top,
+                                   const int32_t* __restrict__ offsets, int E, uint4* __restrict__ out, int cols16) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int slot = blockIdx.x;
+  if (slot >= offsets[E]) return;
+  const int row = perm[slot] / top;
+  for (int c = threadIdx.x; c < cols16; c += blockDim.x) out[(size_t)slot * cols16 + c] = x[(size_t)row * x_stride16 + c];
+}
+
 __device__ __forceinline__ float apply_act(float v, int act) {
   if (act == 1) {            // the square of relu
     v = fmaxf(v, 0.f);
@@ -557,6 +569,15 @@ YALIS_API int yalis_grouped_gemm(const void* a, long a_stride, const int32_t* pe
   if (bm != 32) return YALIS_ERR_SHAPE;
   YALIS_DISPATCH_DTYPE(dtype, T, return yalis_launch(grouped_gemm_simt_kernel<T>, grid, dim3(256), 0, stream, g));
   return YALIS_OK;
+}
+
+// bfloat16 rows of K % 8 == 0 columns on 16-byte boundaries; out contiguous [entries, K].
+YALIS_API int yalis_gather_rows(const void* x, long x_stride, const int32_t* perm, int top, const int32_t* offsets, int E,
+                                void* out, int entries, int K, cudaStream_t stream) {
+  if (entries <= 0) return YALIS_OK;
+  if (K % 8 || x_stride % 8 || ((uintptr_t)x & 15) || ((uintptr_t)out & 15) || top <= 0) return YALIS_ERR_ALIGN;
+  return yalis_launch(gather_rows_kernel, dim3(entries), dim3(K / 8 < 256 ? ((K / 8 + 31) / 32) * 32 : 256), 0, stream,
+                      (const uint4*)x, x_stride / 8, perm, top, offsets, E, (uint4*)out, K / 8);
 }
 
 YALIS_API int yalis_expert_combine(const void* y, long y_stride, const int32_t* inv, const float* weights, int top,

@@ -382,6 +382,171 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   }
 }
 
+// ---- the same product over the experts of a routed feed-forward ---------------------------------------
+// C[slot, :] = act(A[slot, :] . W[expert(slot)]^T) for rows sorted by expert (A holds one row per slot).  A block owns
+// 128 rows of one expert's matrix and one tile of up to NTOK slots of that expert, both named by a plan that an earlier
+// kernel of the step wrote (row tiles as (expert, first slot), their number, the experts' offsets): nothing about the
+// routing is known on the host, so the grid has room for the most tiles the shapes allow and blocks past the last tile
+// leave.  W is one tensor map over all experts' rows [E * N, K]; a box that runs over the end of an expert's rows or
+// of a tile's slots reads neighbours' rows (or zeros past the tensor), which the epilogue does not store.  Unlike the
+// plain product the ring cannot be filled before the preceding kernel has finished: which expert to read is its output.
+struct GroupedParams {
+  __nv_bfloat16* out;   // [slots, N]
+  long long ldo;
+  int N, K, act;        // act 1: the square of relu
+  const int32_t* offsets; const int32_t* tile_expert; const int32_t* tile_slot; const int32_t* n_tiles;
+  int32_t* error;
+};
+
+template <int NTOK>
+__global__ void __launch_bounds__(kThreads, NTOK > 128 ? 1 : 2)
+gemm_grouped_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    const GroupedParams p) {
+  constexpr int STAGES = stages_for<NTOK>();
+  constexpr int KB = kblocks_for<NTOK>();
+  constexpr int A_SUB = TILE_N * TILE_K * 2, B_SUB = NTOK * TILE_K * 2;
+  constexpr int A_BYTES = KB * A_SUB;
+  constexpr int B_BYTES = KB * B_SUB;
+  constexpr int TMEM_COLS = NTOK < 32 ? 32 : NTOK;
+  extern __shared__ __align__(1024) unsigned char smem[];
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem) + 1023) & ~uintptr_t(1023));
+  unsigned char* a_s = base;
+  unsigned char* b_s = base + STAGES * A_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(b_s + STAGES * B_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_d = *tmem_slot;
+
+  pdl_wait();                                         // the plan is the preceding kernels' output
+  const bool active = (int)blockIdx.y < *p.n_tiles;
+  int expert = 0, slot0 = 0, m_rows = 0;
+  if (active) {
+    expert = p.tile_expert[blockIdx.y];
+    slot0 = p.tile_slot[blockIdx.y];
+    m_rows = min(NTOK, p.offsets[expert + 1] - slot0);
+  }
+  const int n0 = blockIdx.x * TILE_N;
+  const int n_kt = active ? (p.K + KB * TILE_K - 1) / (KB * TILE_K) : 0;
+
+  int armed = 0;
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint64_t pol_w = l2_policy_evict_first(), pol_x = l2_policy_evict_last();
+      bool released = false;
+      for (int kt = 0; kt < n_kt; ++kt) {
+        const int s = kt % STAGES;
+        const uint32_t ph = (kt / STAGES) & 1;
+        if (kt >= STAGES && !mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
+        mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb) {
+          const int k = (kt * KB + kb) * TILE_K;
+          tma_load_2d_hint(a_s + s * A_BYTES + kb * A_SUB, &map_w, k, expert * p.N + n0, &full[s], pol_w);
+          tma_load_2d_hint(b_s + s * B_BYTES + kb * B_SUB, &map_x, k, slot0, &full[s], pol_x);
+        }
+        armed = kt + 1;
+        if (kt == n_kt - 2) {
+          pdl_launch_dependents();
+          released = true;
+        }
+      }
+      if (!released) pdl_launch_dependents();
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(NTOK);
+      int kt = 0;
+      for (; kt < n_kt; ++kt) {
+        const int s = kt % STAGES;
+        const uint32_t ph = (kt / STAGES) & 1;
+        if (!mbar_wait(&full[s], ph, abort_flag)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb) {
+          const uint64_t da = umma_desc_sw128(a_s + s * A_BYTES + kb * A_SUB);
+          const uint64_t db = umma_desc_sw128(b_s + s * B_BYTES + kb * B_SUB);
+#pragma unroll
+          for (int j = 0; j < TILE_K / UMMA_K; ++j)
+            umma(tmem_d, da + 2 * j, db + 2 * j, idesc, (kt > 0 || kb > 0 || j > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty[s]);
+      }
+      if (kt == n_kt && n_kt > 0) umma_commit(acc_full);
+    }
+    __syncwarp();
+  } else {
+    const int q = warp & 3;
+    int ok = 1;
+    if (n_kt > 0 && lane == 0) ok = mbar_wait(acc_full, 0, abort_flag) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok && n_kt > 0) {
+      const int n = n0 + q * 32 + lane;
+#pragma unroll
+      for (int c0 = 0; c0 < NTOK; c0 += 16) {
+        if (c0 >= m_rows) break;                       // the same for the whole warp
+        uint32_t r[16];
+        tmem_ld16(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (n < p.N) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int m = c0 + i;
+            if (m < m_rows) {
+              float v = __uint_as_float(r[i]);
+              if (p.act == 1) {
+                v = fmaxf(v, 0.f);
+                v = v * v;
+              }
+              p.out[(size_t)(slot0 + m) * p.ldo + n] = __float2bfloat16_rn(v);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) {
+      atomicOr(p.error, YALIS_FLAG_WAIT_PRODUCT);
+      for (int kt = max(0, armed - STAGES); kt < armed; ++kt) {
+        const int s = kt % STAGES;
+        const uint32_t ph = (kt / STAGES) & 1;
+        for (uint32_t i = 0; i < kSpinLimit; ++i)
+          if (mbar_try_wait(&full[s], ph)) break;
+      }
+    }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(TMEM_COLS));
+  }
+}
+
 // ---- host side ------------------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -473,6 +638,51 @@ template <int NTOK>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, cudaStream_t stream) {
   return p.silu_inter ? launch_cfg<NTOK, true>(mw, mx, p, stream) : launch_cfg<NTOK, false>(mw, mx, p, stream);
 }
+
+template <int NTOK>
+int launch_grouped(const CUtensorMap& mw, const CUtensorMap& mx, const GroupedParams& p, int max_tiles, cudaStream_t stream) {
+  constexpr int STAGES = stages_for<NTOK>();
+  const size_t smem = 1024 + (size_t)STAGES * kblocks_for<NTOK>() * (TILE_N * TILE_K * 2 + NTOK * TILE_K * 2) +
+                      (2 * STAGES + 1) * 8 + 16;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_grouped_kernel<NTOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return YALIS_ERR_LAUNCH;
+    configured = true;
+  }
+  dim3 grid((p.N + TILE_N - 1) / TILE_N, max_tiles);
+  if (grid.y > 65535) return YALIS_ERR_SHAPE;
+  return yalis_launch(gemm_grouped_kernel<NTOK>, grid, dim3(kThreads), smem, stream, mw, mx, p);
+}
+
+}  // namespace
+
+// C[slot, :] = act(A[slot, :] . w[expert(slot)]^T) over a plan's row tiles of `bm` slots (16, 32, 64, 128 or 256):
+// a [rows_a, K] bfloat16 in slot order, w [n_experts, N, K] bfloat16 contiguous, out bfloat16 [rows_a, N].
+YALIS_API int yalis_grouped_gemm_wstream(const void* a, long long lda, int rows_a, const void* w, int n_experts, int N, int K,
+                                         void* out, long long ldo, const int32_t* offsets, const int32_t* tile_expert,
+                                         const int32_t* tile_slot, const int32_t* n_tiles, int max_tiles, int bm, int act,
+                                         int32_t* error, cudaStream_t stream) {
+  if (rows_a <= 0 || max_tiles <= 0 || N <= 0) return YALIS_OK;
+  if (K <= 0 || n_experts <= 0 || (long long)n_experts * N > 0x7fffffffLL) return YALIS_ERR_SHAPE;
+  if ((K % 8) || (lda % 8)) return YALIS_ERR_ALIGN;
+  if (((uintptr_t)a | (uintptr_t)w) & 15) return YALIS_ERR_ALIGN;
+  CUtensorMap mw, mx;
+  if (!make_map(&mw, w, (long long)n_experts * N, K, K, TILE_N) || !make_map(&mx, a, rows_a, K, lda, bm)) return YALIS_ERR_LAUNCH;
+  GroupedParams p;
+  p.out = (__nv_bfloat16*)out; p.ldo = ldo; p.N = N; p.K = K; p.act = act; p.offsets = offsets; p.tile_expert = tile_expert;
+  p.tile_slot = tile_slot; p.n_tiles = n_tiles; p.error = error;
+  switch (bm) {
+    case 16: return launch_grouped<16>(mw, mx, p, max_tiles, stream);
+    case 32: return launch_grouped<32>(mw, mx, p, max_tiles, stream);
+    case 64: return launch_grouped<64>(mw, mx, p, max_tiles, stream);
+    case 128: return launch_grouped<128>(mw, mx, p, max_tiles, stream);
+    case 256: return launch_grouped<256>(mw, mx, p, max_tiles, stream);
+  }
+  return YALIS_ERR_SHAPE;
+}
+
+namespace {
 
 }  // namespace
 

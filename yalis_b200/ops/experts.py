@@ -3,6 +3,7 @@ over all experts, weighted sum).  Nothing here reads the routing on the host."""
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -108,6 +109,44 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, plan: ExpertPlan, *, gather_t
                                    ptr(w), ptr(out), i64(out.stride(0)), i32(dtype_code(a.dtype)), ptr(plan.offsets),
                                    ptr(plan.tile_expert), ptr(plan.tile_slot), ptr(plan.n_tiles), i32(plan.max_tiles),
                                    i32(n_out), i32(k), i32(act), i32(plan.bm), i32(1 if tc else 0), stream()), name)
+    return out
+
+
+WSTREAM_TILES = (16, 32, 64, 128, 256)      # row tiles of the tcgen05 form
+
+
+def wstream_form(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the experts' product takes the tcgen05 form: bfloat16, K a multiple of 8, rows on 16-byte boundaries
+    (``YALIS_B200_NO_GROUPED_TCGEN05=1`` keeps every product on the mma form)."""
+    return os.environ.get("YALIS_B200_NO_GROUPED_TCGEN05", "0") != "1" and tensor_core_form(a, w)
+
+
+def gather_rows(x: torch.Tensor, plan: ExpertPlan, top: int) -> torch.Tensor:
+    """[entries, K]: row ``perm[slot] // top`` of ``x`` for every slot in use (bfloat16, K % 8 == 0)."""
+    name = "gather_rows"
+    need_cuda(name, x)
+    need(x.dim() == 2 and x.dtype == torch.bfloat16 and x.stride(1) == 1 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
+         and x.data_ptr() % 16 == 0, name, "x must be bfloat16 [N, K] with K % 8 == 0 and rows on 16-byte boundaries")
+    out = torch.empty((plan.entries, x.shape[1]), dtype=x.dtype, device=x.device)
+    check(lib().yalis_gather_rows(ptr(x), i64(x.stride(0)), ptr(plan.perm), i32(top), ptr(plan.offsets),
+                                  i32(plan.offsets.numel() - 1), ptr(out), i32(plan.entries), i32(x.shape[1]), stream()), name)
+    return out
+
+
+def grouped_gemm_wstream(a: torch.Tensor, w: torch.Tensor, plan: ExpertPlan, *, act: int = ACT_NONE) -> torch.Tensor:
+    """C[s, :] = act(A[s, :] . w[expert(s)]^T) on tcgen05 tensor cores with TMA-streamed operands: ``a`` [entries, K]
+    holds one row per slot (see ``gather_rows``), ``w`` [E, n_out, K]; the plan's row tile is one of ``WSTREAM_TILES``."""
+    name = "grouped_gemm_wstream"
+    need_cuda(name, a, w)
+    need(a.dim() == 2 and w.dim() == 3 and w.is_contiguous() and a.shape == (plan.entries, w.shape[2]) and a.stride(1) == 1
+         and tensor_core_form(a, w) and plan.bm in WSTREAM_TILES, name,
+         "A bfloat16 [entries, K] in slot order, w bfloat16 [E, n_out, K], K % 8 == 0, a row tile the kernel has")
+    out = torch.empty((plan.entries, w.shape[1]), dtype=a.dtype, device=a.device)
+    from ._lib import error_word
+    check(lib().yalis_grouped_gemm_wstream(ptr(a), i64(a.stride(0)), i32(plan.entries), ptr(w), i32(w.shape[0]), i32(w.shape[1]),
+                                           i32(w.shape[2]), ptr(out), i64(out.stride(0)), ptr(plan.offsets), ptr(plan.tile_expert),
+                                           ptr(plan.tile_slot), ptr(plan.n_tiles), i32(plan.max_tiles), i32(plan.bm), i32(act),
+                                           ptr(error_word(a.device)), stream()), name)
     return out
 
 

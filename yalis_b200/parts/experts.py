@@ -75,22 +75,36 @@ class RoutedExperts(FeedForward):
         unused = self.n_experts * (1.0 - self.top / self.n_experts) ** tokens
         return unused * (self.w_up[0].numel() + self.w_down[0].numel()) * self.w_up.element_size()
 
-    def row_tile(self, x: torch.Tensor) -> int:
-        """Rows of a tile of the experts' products.  Where the tensor-core form runs: 128 when an expert gets about that
-        many tokens on average, 16 when it gets at most 8 (a decode step: small tiles leave shared memory to a deeper
-        ring of weight tiles), else 32.  The other form has tiles of 32."""
-        tc = (x.dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.inner % 8 == 0 and x.stride(0) % 8 == 0
-              and x.data_ptr() % 16 == 0)
-        if not tc:
-            return 32
+    def _aligned(self, x: torch.Tensor) -> bool:
+        return (x.dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.inner % 8 == 0 and x.stride(0) % 8 == 0
+                and x.data_ptr() % 16 == 0)
+
+    def row_tile(self, x: torch.Tensor, wstream: bool) -> int:
+        """Rows of a tile of the experts' products, from the step's shape alone.  tcgen05 form: the smallest of 16 ... 256
+        that holds twice the rows an expert gets on average (a tile is the N side of the MMA: a half-empty one costs
+        nothing where the weights set the pace, and few experts then need a second tile).  mma form: 128 when an
+        expert gets about that many, 16 when at most 8, else 32.  The float32 form has tiles of 32."""
         entries = x.shape[0] * self.top
+        if wstream:
+            for tile in ops.WSTREAM_TILES:
+                if 2 * entries <= tile * self.n_experts:
+                    return tile
+            return ops.WSTREAM_TILES[-1]
+        if not self._aligned(x):
+            return 32
         return 128 if entries >= 96 * self.n_experts else (16 if entries <= 8 * self.n_experts else 32)
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         ids, weights = ops.route(x, self.router, self.top, self.eps, ctx.req_of_token if ctx is not None else None)
-        plan = ops.expert_plan(ids, self.n_experts, self.row_tile(x))
-        inner = ops.grouped_gemm(x, self.w_up, plan, gather_top=self.top, act=_GROUPED_ACT[self.act])
-        y = ops.grouped_gemm(inner, self.w_down, plan)
+        wstream = self._aligned(x) and ops.wstream_form(x, self.w_up)
+        plan = ops.expert_plan(ids, self.n_experts, self.row_tile(x, wstream))
+        if wstream:
+            rows = ops.gather_rows(x, plan, self.top)
+            inner = ops.grouped_gemm_wstream(rows, self.w_up, plan, act=_GROUPED_ACT[self.act])
+            y = ops.grouped_gemm_wstream(inner, self.w_down, plan)
+        else:
+            inner = ops.grouped_gemm(x, self.w_up, plan, gather_top=self.top, act=_GROUPED_ACT[self.act])
+            y = ops.grouped_gemm(inner, self.w_down, plan)
         shared = None
         if self.shared is not None:
             shared = linear(activation(linear(x, self.s_up), self.act), self.s_down)
