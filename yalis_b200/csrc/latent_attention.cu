@@ -277,7 +277,8 @@ __global__ void __launch_bounds__(128 * WR) latent_attention_mma_kernel(const La
   pdl_wait();
   const int req = blockIdx.y;
   const int q0 = a.q_start[req], q_len = a.q_start[req + 1] - q0;
-  const int n_rows = q_len * a.heads, row0 = blockIdx.x * BM;
+  // the last tiles of a portion see the most rows: they go first, so that the launch does not end on its longest blocks
+  const int n_rows = q_len * a.heads, row0 = (int)(gridDim.x - 1 - blockIdx.x) * BM;
   if (row0 >= n_rows) return;
   const int rows_here = min(BM, n_rows - row0);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gq = lane >> 2, tq = lane & 3;
@@ -345,19 +346,22 @@ __global__ void __launch_bounds__(128 * WR) latent_attention_mma_kernel(const La
     // scores of this warp's 16 rows for its group's 32 queries
     float s[2][2][4] = {}, s2[2][2][4] = {};           // even and odd steps of K apart: twice the MMAs in flight
     for (int k0 = 0; k0 < W; k0 += 16) {
-      uint32_t af[2][4];
+      uint32_t af[2][4], bq[4];                     // fragments by ldmatrix: three instructions feed four MMAs
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
-        const __nv_bfloat16* qp = Qs + (rb + mt * 16 + gq) * LD + k0 + 2 * tq;
-        af[mt][0] = *reinterpret_cast<const uint32_t*>(qp);
-        af[mt][1] = *reinterpret_cast<const uint32_t*>(qp + 8 * LD);
-        af[mt][2] = *reinterpret_cast<const uint32_t*>(qp + 8);
-        af[mt][3] = *reinterpret_cast<const uint32_t*>(qp + 8 * LD + 8);
+        const unsigned addr = (unsigned)__cvta_generic_to_shared(Qs + (rb + mt * 16 + (lane & 15)) * LD + k0 + (lane >> 4) * 8);
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(af[mt][0]), "=r"(af[mt][1]), "=r"(af[mt][2]), "=r"(af[mt][3]) : "r"(addr));
+      }
+      {
+        const unsigned addr = (unsigned)__cvta_generic_to_shared(
+            Kt + (wc * 16 + (lane & 7) + ((lane >> 4) << 3)) * LD + k0 + ((lane >> 3) & 1) * 8);
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(bq[0]), "=r"(bq[1]), "=r"(bq[2]), "=r"(bq[3]) : "r"(addr));
       }
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
-        const __nv_bfloat16* kp = Kt + (wc * 16 + nt * 8 + gq) * LD + k0 + 2 * tq;
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kp), b1 = *reinterpret_cast<const uint32_t*>(kp + 8);
+        const uint32_t b0 = bq[2 * nt], b1 = bq[2 * nt + 1];
 #pragma unroll
         for (int mt = 0; mt < 2; ++mt) {
           if (k0 & 16) mma_bf16(s2[mt][nt], af[mt], b0, b1);
@@ -439,19 +443,31 @@ __global__ void __launch_bounds__(128 * WR) latent_attention_mma_kernel(const La
       uint32_t ah[2][4], al[2][4];
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
-        const int off = (rb + mt * 16 + gq) * LDP + kk + 2 * tq;
-        ah[mt][0] = *reinterpret_cast<const uint32_t*>(Ph + off);
-        ah[mt][1] = *reinterpret_cast<const uint32_t*>(Ph + off + 8 * LDP);
-        ah[mt][2] = *reinterpret_cast<const uint32_t*>(Ph + off + 8);
-        ah[mt][3] = *reinterpret_cast<const uint32_t*>(Ph + off + 8 * LDP + 8);
-        al[mt][0] = *reinterpret_cast<const uint32_t*>(Pl + off);
-        al[mt][1] = *reinterpret_cast<const uint32_t*>(Pl + off + 8 * LDP);
-        al[mt][2] = *reinterpret_cast<const uint32_t*>(Pl + off + 8);
-        al[mt][3] = *reinterpret_cast<const uint32_t*>(Pl + off + 8 * LDP + 8);
+        const int off = (rb + mt * 16 + (lane & 15)) * LDP + kk + (lane >> 4) * 8;
+        const unsigned addr_h = (unsigned)__cvta_generic_to_shared(Ph + off), addr_l = (unsigned)__cvta_generic_to_shared(Pl + off);
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(ah[mt][0]), "=r"(ah[mt][1]), "=r"(ah[mt][2]), "=r"(ah[mt][3]) : "r"(addr_h));
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(al[mt][0]), "=r"(al[mt][1]), "=r"(al[mt][2]), "=r"(al[mt][3]) : "r"(addr_l));
       }
+      // rows kk .. kk + 15 of the tile as the B operand, transposed on the way: two 8-column tiles a load
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        // rows kk .. kk + 15 of the tile, 8 columns: lanes 0-15 name the 16 row starts
+      for (int np = 0; np < NT / 2; ++np) {
+        const __nv_bfloat16* vp = Kt + (kk + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + wc * (R / 4) + np * 16 + (lane >> 4) * 8;
+        uint32_t b[4];
+        const unsigned addr = (unsigned)__cvta_generic_to_shared(vp);
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]) : "r"(addr));
+#pragma unroll
+        for (int half = 0; half < 2; ++half)
+#pragma unroll
+          for (int mt = 0; mt < 2; ++mt) {
+            mma_bf16(o[mt][2 * np + half], ah[mt], b[2 * half], b[2 * half + 1]);
+            mma_bf16(o[mt][2 * np + half], al[mt], b[2 * half], b[2 * half + 1]);
+          }
+      }
+      if constexpr (NT % 2) {                       // an odd tile left over (r = 96)
+        constexpr int nt = NT - 1;
         const __nv_bfloat16* vp = Kt + (kk + (lane & 15)) * LD + wc * (R / 4) + nt * 8;
         uint32_t b0, b1;
         const unsigned addr = (unsigned)__cvta_generic_to_shared(vp);
