@@ -97,11 +97,6 @@ class LatentAttention(Mixer, Projected):
     def cache_request(self) -> PagedKV:
         return PagedKV(1, self.r + self.p, self.cache_window, v_head_dim=0)
 
-    # A bfloat16 step whose shapes the tensor-core attention takes runs the two per-head maps as batched library
-    # products (measured at 8 tokens, 16 heads of 128 x 256: 41 us on the engine's own kernel, which stays the
-    # float32 path's and that of other shapes).
-    BATCHED_FROM = 1
-
     def _tensor_core_form(self, dtype: torch.dtype) -> bool:
         return dtype == torch.bfloat16 and ops.mma_supports(self.r, self.p)
 
@@ -135,9 +130,10 @@ class LatentAttention(Mixer, Projected):
                            ctx.req_of_token, bad_flag=ctx.error_flag)
         q = z[:, self.q_off:self.q_off + nh * (d + p)].unflatten(1, (nh, d + p))
         gate = z[:, self.g_off:self.g_off + nh * e] if self.gate else None
-        tensor_cores = self._tensor_core_form(z.dtype)
-        if tensor_cores and n >= self.BATCHED_FROM:
-            # absorbed queries, attention and values head-major [H, N, .] in bfloat16: the operands of batched products
+        if self._tensor_core_form(z.dtype):
+            # bfloat16 rows of a shape the tensor-core attention takes: the two per-head maps are batched library
+            # products (at 8 tokens, 16 heads of 128 x 256, the engine's own kernel took 41 us a map, the library 4),
+            # with the absorbed queries, the attention's result and the values head-major [H, N, .] in bfloat16
             q_lat = torch.bmm(q[:, :, :d].transpose(0, 1), self.uk)                       # [H, N, r]
             mixed = torch.empty((nh, n, r), dtype=z.dtype, device=z.device)
             ops.latent_attention_mma(q_lat.transpose(0, 1), qc[:, :, r:], mixed.transpose(0, 1), cache.k, ctx.positions,
@@ -149,14 +145,9 @@ class LatentAttention(Mixer, Projected):
             else:
                 y.unflatten(1, (nh, e)).copy_(o.transpose(0, 1))
             return
+        # the float32 path, and shapes the tensor-core form does not take: exact kernels throughout
         ops.head_project(q[:, :, :d], self.uk_t, qc[:, :, :r], req_of_token=ctx.req_of_token)
-        if tensor_cores:
-            mixed = torch.empty((n, nh, r), dtype=torch.float32, device=z.device)
-            ops.latent_attention_mma(qc[:, :, :r], qc[:, :, r:], mixed, cache.k, ctx.positions, ctx.q_start, ctx.req_of_token,
-                                     table, ctx.n_requests, ctx.host.max_q_len, self.scale, self.window,
-                                     n_splits=self._splits(ctx))
-        else:
-            mixed = ops.latent_attention_exact(qc, cache.k, ctx.positions, ctx.req_of_token, table, r, self.scale, self.window)
+        mixed = ops.latent_attention_exact(qc, cache.k, ctx.positions, ctx.req_of_token, table, r, self.scale, self.window)
         ops.head_project(mixed, self.uv, y.unflatten(1, (nh, e)), gate=gate, req_of_token=ctx.req_of_token)
 
     def forward(self, x: torch.Tensor, ctx, cache: PagedKVCache) -> torch.Tensor:
