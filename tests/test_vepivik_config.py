@@ -49,7 +49,7 @@ def test_page_groups_by_how_long_rows_are_kept():
     assert set(groups) == {"kv_window_33", "kv_window_9", "kv_window_16", "kv_window_11"}
 
 
-@pytest.mark.parametrize("dims, base, factor, original, fast, slow", [(16, 10000.0, 2.0, 512, 32.0, 1.0), (8, 100.0, 4.0, 32, 8.0, 2.0),
+@pytest.mark.parametrize("dims, base, factor, original, fast, slow", [(24, 5000.0, 3.0, 1024, 24.0, 1.5), (8, 100.0, 4.0, 32, 8.0, 2.0),
                                                                       (4, 20.0, 3.0, 16, 4.0, 0.5), (32, 500000.0, 40.0, 8192, 32.0, 1.0)])
 def test_yarn_frequencies_against_the_plain_ones(dims, base, factor, original, fast, slow):
     rot = {"dims": dims, "base": base, "scaling": {"factor": factor, "original": original, "fast": fast, "slow": slow}}
